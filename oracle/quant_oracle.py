@@ -1,0 +1,255 @@
+"""CPU oracle for torch_npu's quantized-inference operator path.
+
+TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA kernels are compared
+with; nothing in the shipped package imports it.  Only the test-suite, the smoke
+check and the CPU-baseline leg of the benchmark may call it.
+
+The arithmetic of the four operators lives in the un-vendored ``op-plugin``
+submodule of the reference (``.gitmodules:1-4``, no commit pinned) and, below
+that, in closed aclnn kernels.  What follows therefore restates the algorithm
+from the CPU golden compositions the reference keeps in its own tests:
+
+* symmetric int8 quantisation ``scale = max/127``, ``round`` (half to even),
+  ``clip(-128, 127)``: ``test/custom_ops/test_npu_ifmr.py:38-45``,
+  ``test/contrib/test_linear_weight_quant.py:13-16``; rounding mode "rint":
+  ``torch_npu/contrib/module/quant_conv2d.py:101``.
+* int8 GEMM dequantisation ``x1_scale * x2_scale * (x1 @ x2)`` with the bias
+  added to the accumulator before scaling:
+  ``test/distributed/tensor/test_matrix_ops.py:28-37,93-110``.
+* weight-only dequantisation ``(w + offset) * scale`` followed by an fp32
+  matmul and a cast: ``test/contrib/test_linear_weight_quant.py:20-28``,
+  ``test/custom_ops/test_npu_anti_quant.py:29-42``.
+* int4 nibble order inside an int32 (low nibble first, sign-extended):
+  ``test/custom_ops/test_npu_anti_quant.py:12-24``.
+
+PARITY STATUS: the reference holds no known-answer vectors for
+``npu_dynamic_quant``, ``npu_quant_matmul``, ``npu_convert_weight_to_int4pack``
+or group-wise W4A16 -> for those ops parity is UNPINNED.  Pinned pieces: the
+int4 unpack convention, the ``(w+offset)*scale`` weight-only golden and the
+``x1_scale*x2_scale*(x1@x2)`` dequant golden, all three checked against the
+reference's own helper functions through ``tests/golden/reference_goldens.npz``.
+
+Every float step below is done in IEEE binary32 with numpy (one rounding per
+operation, no fused multiply-add), in the order the CUDA kernels use, so that
+integer outputs and fp32 scales can be compared bit for bit.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+F32 = np.float32
+
+
+def _to_f32(t) -> np.ndarray:
+    """bf16/fp16/fp32 torch tensor (or ndarray) -> float32 ndarray, exact."""
+    if isinstance(t, torch.Tensor):
+        return t.detach().cpu().to(torch.float32).numpy()
+    return np.asarray(t, dtype=F32)
+
+
+def _cast_out(a: np.ndarray, dtype: torch.dtype) -> torch.Tensor:
+    """float32 ndarray -> torch tensor of ``dtype`` (round to nearest even)."""
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=F32)).to(dtype)
+
+
+# --------------------------------------------------------------------------- A1
+def dynamic_quant(x, smooth_scales=None):
+    """``npu_dynamic_quant(input, smooth_scales=None)`` -> (int8 y, fp32 scale).
+
+    Per row of the last dimension: ``xs = x * smooth`` (fp32), ``amax = max|xs|``,
+    ``scale = amax / 127`` (true division), ``y = clip(rint(xs / scale), -128, 127)``.
+    An all-zero row gives ``scale = 0`` and ``y = 0``.  Output contract
+    (int8 of the input's shape, fp32 of ``shape[:-1]``):
+    ``test/test_fake_tensor.py:1671-1686``; formula: see the module docstring.
+    """
+    xs = _to_f32(x)
+    if smooth_scales is not None:
+        xs = xs * _to_f32(smooth_scales)            # fp32 multiply, one rounding
+    amax = np.max(np.abs(xs), axis=-1) if xs.shape[-1] else np.zeros(xs.shape[:-1], F32)
+    scale = (amax / F32(127.0)).astype(F32)
+    safe = np.where(scale == 0, F32(1.0), scale)[..., None]
+    with np.errstate(invalid="ignore", over="ignore"):
+        q = np.rint(xs / safe)
+    q = np.where(scale[..., None] == 0, F32(0.0), q)
+    y = np.clip(q, -128, 127).astype(np.int8)
+    return torch.from_numpy(y), torch.from_numpy(scale.astype(F32))
+
+
+# --------------------------------------------------------------------------- A2
+def int8_gemm_int32(x1: torch.Tensor, x2: torch.Tensor) -> np.ndarray:
+    """Exact ``x1 @ x2`` for int8 operands, int32 result.
+
+    Runs as a float64 GEMM: every product and partial sum is an integer below
+    2**53 (|acc| <= 128*128*K), so the result is exact in any summation order.
+    """
+    a = x1.detach().cpu().to(torch.float64)
+    b = x2.detach().cpu().to(torch.float64)
+    return torch.matmul(a, b).numpy().astype(np.int64).astype(np.int32)
+
+
+def quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None,
+                 output_dtype=None):
+    """``npu_quant_matmul``: int8 x int8 -> int32, fused dequantisation.
+
+    ``acc = x1 @ x2 (+ int32 bias[n])``; int32 output returns ``acc``.  Otherwise
+    ``v = float(acc) * scale[n]``, then ``* pertoken_scale[m]`` if given, then
+    a floating bias is added, then ``+ offset[n]`` if given; each step one fp32
+    rounding; ``v`` is cast to bf16/fp16 (nearest even) or, for int8 (the default),
+    ``clip(rint(v), -128, 127)``.  Dequant order follows
+    ``test/distributed/tensor/test_matrix_ops.py:28-37`` (bias before scaling);
+    output dtypes ``test/test_fake_tensor.py:1884-1925``.
+    """
+    out_dtype = torch.int8 if output_dtype is None else output_dtype
+    acc = int8_gemm_int32(x1, x2)                                   # [..., M, N]
+    n = acc.shape[-1]
+    fbias = None
+    if bias is not None:
+        if bias.dtype == torch.int32:
+            acc = (acc.astype(np.int64) + bias.detach().cpu().numpy().astype(np.int64)
+                   .reshape(bias.shape if bias.dim() > 1 else (n,))).astype(np.int32)
+        else:
+            fbias = _to_f32(bias).reshape(bias.shape if bias.dim() > 1 else (n,))
+    if out_dtype == torch.int32:
+        return torch.from_numpy(acc)
+    if scale.dtype == torch.int64:
+        sc = trans_quant_param_decode(scale)[0]
+    else:
+        sc = _to_f32(scale)
+    v = acc.astype(F32) * sc.reshape(-1)                            # int32->fp32 RNE, then mul
+    if pertoken_scale is not None:
+        pt = _to_f32(pertoken_scale).reshape(-1)
+        v = (v.reshape(-1, n) * pt[:, None]).reshape(acc.shape)
+    if fbias is not None:
+        v = v + fbias
+    if offset is not None:
+        v = v + _to_f32(offset).reshape(-1)
+    v = v.astype(F32)
+    if out_dtype == torch.int8:
+        return torch.from_numpy(np.clip(np.rint(v), -128, 127).astype(np.int8))
+    return _cast_out(v, out_dtype)
+
+
+def trans_quant_param(scale, offset=None):
+    """``npu_trans_quant_param(scale, offset=None)`` -> int64 dequant parameter.
+
+    Shape/dtype contract: ``test/test_fake_tensor.py:1929-1943`` (result has the
+    broadcast shape of scale and offset, dtype int64).  The bit layout is not
+    present in the reference tree; the layout used here keeps the fp32 bit
+    pattern of ``scale`` in bits [0,32) and leaves the upper word zero.  The
+    offset stays a separate fp32 argument of ``npu_quant_matmul`` (that is how
+    ``torch_npu/contrib/module/linear_quant.py:110-112`` passes it), so it only
+    contributes its shape.
+    """
+    s = _to_f32(scale)
+    shape = s.shape
+    if offset is not None:
+        shape = np.broadcast_shapes(s.shape, tuple(offset.shape))
+    bits = np.broadcast_to(s, shape).astype(F32).view(np.uint32).astype(np.int64)
+    return torch.from_numpy(np.ascontiguousarray(bits))
+
+
+def trans_quant_param_decode(param):
+    bits = param.detach().cpu().numpy().astype(np.int64)
+    lo = (bits & 0xFFFFFFFF).astype(np.uint32)
+    return np.ascontiguousarray(lo).view(F32).reshape(-1), None
+
+
+# --------------------------------------------------------------------------- A4
+def convert_weight_to_int4pack(w: torch.Tensor) -> torch.Tensor:
+    """Pack int4 values (one per int32 element, range [-8, 7]) eight per int32
+    along the last dimension; element ``j`` of each group of eight occupies bits
+    ``[4j, 4j+4)``.  Inverse of ``unpack_int4`` below."""
+    a = w.detach().cpu().numpy().astype(np.int64)
+    if a.shape[-1] % 8:
+        raise ValueError("last dimension must be a multiple of 8")
+    if a.min(initial=0) < -8 or a.max(initial=0) > 7:
+        raise ValueError("int4 values must lie in [-8, 7]")
+    g = (a & 0xF).reshape(*a.shape[:-1], a.shape[-1] // 8, 8)
+    packed = np.zeros(g.shape[:-1], dtype=np.int64)
+    for j in range(8):
+        packed |= g[..., j] << (4 * j)
+    return torch.from_numpy(packed.astype(np.uint32).view(np.int32).reshape(g.shape[:-1]))
+
+
+def unpack_int4(p: torch.Tensor) -> torch.Tensor:
+    """int32 [..., N/8] -> int8 [..., N]: bytes in memory order, low nibble first,
+    nibbles sign-extended (``test/custom_ops/test_npu_anti_quant.py:12-24``)."""
+    a = np.ascontiguousarray(p.detach().cpu().numpy().astype(np.int32))
+    b = a.view(np.uint8).reshape(*a.shape, 4)
+    lo = (b & 0xF).astype(np.int8)
+    hi = (b >> 4).astype(np.int8)
+    nib = np.stack([lo, hi], axis=-1).reshape(*a.shape[:-1], a.shape[-1] * 8)
+    return torch.from_numpy(np.where(nib > 7, nib - 16, nib).astype(np.int8))
+
+
+# --------------------------------------------------------------------------- A3
+def dequant_weight(weight, antiquant_scale, antiquant_offset=None, antiquant_group_size=0,
+                   dequant_dtype=None):
+    """fp32 ``(w + offset) * scale`` of an int8 ``[K,N]`` or int4-packed int32
+    ``[K,N/8]`` weight.  Scale/offset are per channel (``[N]`` / ``[1,N]``) or per
+    group of ``antiquant_group_size`` rows of K (``[K/gs, N]``).  ``dequant_dtype``
+    (fp16/bf16) rounds the sum and the product to that type, which is what the
+    reference's golden does when it is handed fp16 tensors
+    (``test/contrib/test_linear_weight_quant.py:21-26``); the default keeps fp32."""
+    w = unpack_int4(weight) if weight.dtype == torch.int32 else weight.detach().cpu()
+    if dequant_dtype is not None:
+        k, n = w.shape[-2], w.shape[-1]
+        wl = w.to(dequant_dtype)
+        if antiquant_offset is not None:
+            wl = wl + antiquant_offset.detach().cpu().to(dequant_dtype).reshape(-1, n)
+        wl = wl * antiquant_scale.detach().cpu().to(dequant_dtype).reshape(-1, n)
+        return wl.to(torch.float32).numpy()
+    w = w.to(torch.float32).numpy()
+    k, n = w.shape[-2], w.shape[-1]
+
+    def expand(p):
+        a = _to_f32(p)
+        if a.ndim == 2 and a.shape[0] > 1:
+            gs = antiquant_group_size if antiquant_group_size > 0 else k // a.shape[0]
+            a = np.repeat(a, gs, axis=0)[:k]
+        return a.reshape(-1, n) if a.ndim <= 2 else a
+
+    if antiquant_offset is not None:
+        w = w + expand(antiquant_offset)
+    return (w * expand(antiquant_scale)).astype(F32)
+
+
+def weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=None,
+                             quant_scale=None, quant_offset=None, bias=None,
+                             antiquant_group_size=0, inner_precise=0, dequant_dtype=None):
+    """``npu_weight_quant_batchmatmul``: ``x @ ((w + offset) * scale) (+ bias)``,
+    result in ``x.dtype`` (``test/contrib/test_linear_weight_quant.py:20-28``).
+    The product is accumulated in float64 and rounded once to fp32 so that the
+    value does not depend on the host's summation order."""
+    if quant_scale is not None or quant_offset is not None or inner_precise != 0:
+        raise NotImplementedError("requantised output / inner_precise are outside the path")
+    wd = dequant_weight(weight, antiquant_scale, antiquant_offset, antiquant_group_size, dequant_dtype)
+    xf = x.detach().cpu().to(torch.float64)
+    out = torch.matmul(xf, torch.from_numpy(wd).to(torch.float64)).to(torch.float32).numpy()
+    if bias is not None:
+        out = out + _to_f32(bias).reshape(-1)
+    return _cast_out(out, x.dtype)
+
+
+# ------------------------------------------------------------------ comparison
+def max_mixed_error(actual: torch.Tensor, expected: torch.Tensor) -> float:
+    """Largest per-element ``min(|d|, |d| / max(|a|, |e|))``: the atol-OR-rtol rule of
+    ``torch_npu/testing/testcase.py:161-175`` expressed as one number, to be held
+    against a single bound (2**-7 for bf16/fp16 outputs)."""
+    a = actual.detach().cpu().to(torch.float64)
+    e = expected.detach().cpu().to(torch.float64)
+    d = (a - e).abs()
+    den = torch.maximum(a.abs(), e.abs()).clamp_min(1e-30)
+    return float(torch.minimum(d, d / den).max()) if d.numel() else 0.0
+
+
+def count_outside(actual, expected, prec: float, floor: float = 6e-8):
+    """Element counts failing the absolute and the relative criterion of the
+    reference's ``assertRtolEqual`` (``torch_npu/testing/testcase.py:161-175``): that
+    helper fails only when BOTH counts exceed ``size * prec``."""
+    a = actual.detach().cpu().to(torch.float64).numpy()
+    e = expected.detach().cpu().to(torch.float64).numpy()
+    d = np.abs(a - e)
+    den = np.maximum(np.abs(a), np.abs(e)) + floor
+    return int((d > prec).sum()), int((d / den > prec).sum())
