@@ -1,0 +1,131 @@
+/* b200q.h - C ABI of the B200 (sm_100a) quantized-inference kernels.
+ *
+ * These entry points are what a binding of torch_npu's quantized-inference operator
+ * path calls in place of the op-plugin OpApi functions and the aclnn kernels behind
+ * them.  Reference interfaces are cited by the path of the file inside Ascend/pytorch.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless it says "host"; tensors are row-major;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued, never synchronised;
+ *   - functions return a b200q_status; b200q_last_error() gives the thread's last message;
+ *   - the library allocates no device memory: scratch is passed in by the caller and sized
+ *     by the matching *_workspace_bytes() query;
+ *   - there is no CPU fallback: without a CUDA device every compute call fails.
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  B200Q_OK = 0,
+  B200Q_ERR_BAD_ARG = 1,      /* null pointer, negative size, misaligned buffer, bad enum   */
+  B200Q_ERR_UNSUPPORTED = 2,  /* valid request outside what the path implements            */
+  B200Q_ERR_LAUNCH = 3,       /* CUDA reported an error at launch                           */
+  B200Q_ERR_WORKSPACE = 4,    /* workspace missing or smaller than *_workspace_bytes()      */
+  B200Q_ERR_DEVICE = 5        /* a kernel recorded a device-side error (see device_error)   */
+} b200q_status;
+
+typedef enum {
+  B200Q_BF16 = 0,
+  B200Q_F16 = 1,
+  B200Q_F32 = 2,
+  B200Q_I8 = 3,
+  B200Q_I32 = 4,
+  B200Q_I64 = 5,  /* npu_trans_quant_param encoding: fp32 bit pattern in the low word */
+  B200Q_NONE = -1
+} b200q_dtype;
+
+/* Library version (major*10000 + minor*100 + patch) and the last error text of the calling thread. */
+int b200q_version(void);
+const char* b200q_last_error(void);
+const char* b200q_status_string(int status);
+
+/* Reads (and, if `reset` != 0, clears) the device-side error word of the current device.
+ * 0 means no kernel gave up a bounded wait.  Synchronises the device. */
+int b200q_device_error(unsigned int* code, int reset);
+
+/* npu_dynamic_quant(input, smooth_scales=None) -> (int8 y, fp32 scale)
+ *   replaces op_plugin::npu_dynamic_quant / aclnn DynamicQuant, reached from
+ *   torch_npu/onnx/wrapper_onnx_ops.py:743-745; output contract test/test_fake_tensor.py:1671-1686.
+ * x [rows,k] bf16 or f16; smooth [k] (f32 or x's dtype) or NULL; y int8 [rows,k]; scale f32 [rows].
+ * Per row: xs = x*smooth (fp32), scale = max|xs| / 127, y = clamp(rint(xs/scale), -128, 127);
+ * an all-zero row gives scale 0 and y 0. */
+int b200q_dynamic_quant(const void* x, int x_dtype, const void* smooth, int smooth_dtype, int8_t* y,
+                        float* scale, int64_t rows, int64_t k, void* stream);
+
+/* npu_quant_matmul(x1, x2, scale, *, offset, pertoken_scale, bias, output_dtype)
+ *   replaces op_plugin::npu_quant_matmul / aclnnQuantMatmulV3-V4, reached from
+ *   torch_npu/contrib/module/linear_quant.py:110-112 and linear_a8w8_quant.py:117-120.
+ * out[m,n] = cast( float(sum_k x1[m,k]*x2[k,n] + bias_i32[n]) * scale[n] * pertoken[m]
+ *                  + bias_float[n] + offset[n] );  int32 output returns the accumulator. */
+typedef struct {
+  const int8_t* x1;        /* [m,k], row stride k                                             */
+  const int8_t* x2;        /* element (k_,n_) at x2[k_*x2_stride_k + n_*x2_stride_n]          */
+  int64_t m, k, n;
+  int64_t x2_stride_k;     /* 1 for the transposed view of an [n,k] weight (what the modules  */
+  int64_t x2_stride_n;     /*   pass); n and 1 for a contiguous [k,n] weight                  */
+  const void* scale;       /* [scale_len], scale_len = 1 or n; f32, bf16 or i64               */
+  int scale_dtype;
+  int64_t scale_len;
+  const float* offset;     /* [offset_len] (1 or n) or NULL                                   */
+  int64_t offset_len;
+  const float* pertoken_scale; /* [m] or NULL                                                 */
+  const void* bias;        /* [n] or NULL; i32 joins the accumulator, bf16/f16/f32 are added
+                              after the scales                                                */
+  int bias_dtype;
+  void* out;               /* [m,n], row stride n                                             */
+  int out_dtype;           /* B200Q_I8, B200Q_F16, B200Q_BF16 or B200Q_I32                    */
+  void* workspace;         /* >= b200q_quant_matmul_workspace_bytes(), 256-byte aligned       */
+  size_t workspace_bytes;
+} b200q_quant_matmul_args;
+
+size_t b200q_quant_matmul_workspace_bytes(int64_t m, int64_t k, int64_t n, int64_t x2_stride_k,
+                                          int64_t x2_stride_n);
+int b200q_quant_matmul(const b200q_quant_matmul_args* args, void* stream);
+
+/* npu_weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset, ..., antiquant_group_size)
+ *   replaces op_plugin::npu_weight_quant_batchmatmul / aclnnWeightQuantBatchMatmulV2, reached from
+ *   torch_npu/contrib/module/linear_weight_quant.py:106-109.
+ * out = x @ ((w + antiquant_offset) * antiquant_scale) (+ bias), result in x's dtype. */
+typedef struct {
+  const void* x;           /* [m,k] bf16 or f16, row stride k                                 */
+  int x_dtype;
+  const void* weight;      /* int8: element (k_,n_) at weight[k_*w_stride_k + n_*w_stride_n];
+                              int4: int32 [k, n/8] contiguous, 8 values per word, value j of a
+                              word in bits [4j, 4j+4)                                         */
+  int weight_bits;         /* 8 or 4                                                          */
+  int64_t m, k, n;
+  int64_t w_stride_k, w_stride_n; /* int8 only                                                */
+  const void* antiquant_scale;    /* [groups, n] in x's dtype, row stride n; groups = 1 or k/group_size */
+  const void* antiquant_offset;   /* same shape or NULL                                       */
+  int64_t group_size;      /* 0 = per channel                                                 */
+  const void* bias;        /* [n] in x's dtype, or NULL                                       */
+  void* out;               /* [m,n] in x's dtype                                              */
+  void* workspace;
+  size_t workspace_bytes;
+} b200q_weight_quant_matmul_args;
+
+size_t b200q_weight_quant_matmul_workspace_bytes(int64_t m, int64_t k, int64_t n, int weight_bits);
+int b200q_weight_quant_matmul(const b200q_weight_quant_matmul_args* args, void* stream);
+
+/* npu_convert_weight_to_int4pack(weight): int32 [rows, cols] holding one int4 value each
+ * -> int32 [rows, cols/8]; value j of each group of eight goes to bits [4j, 4j+4).
+ *   The operator does not occur in the reference tree; the nibble order is the one its
+ *   unpack helper expects, test/custom_ops/test_npu_anti_quant.py:12-24. */
+int b200q_int4pack(const int32_t* w, int32_t* packed, int64_t rows, int64_t cols, void* stream);
+
+/* npu_trans_quant_param(scale, offset=None): fp32 scale -> int64 dequant parameter
+ *   (torch_npu/contrib/module/linear_quant.py:107-108; contract test/test_fake_tensor.py:1929-1943).
+ * out[i] = bit pattern of scale[i % scale_len] in the low word, upper word 0. */
+int b200q_trans_quant_param(const float* scale, int64_t scale_len, int64_t* out, int64_t out_len, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

@@ -1,0 +1,223 @@
+"""ctypes binding of ``include/b200q.h``.
+
+This is the same boundary a binding in any other host language would use: plain device
+pointers, sizes and enums.  The helpers below take torch CUDA tensors only to obtain those
+pointers (``data_ptr()``) and the current stream; they allocate outputs and workspace with
+torch and pass them down.  There is no CPU path: loading fails loudly when the library has
+not been built, and every compute call needs a CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libb200q.so")
+
+OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_WORKSPACE, ERR_DEVICE = range(6)
+BF16, F16, F32, I8, I32, I64, NONE = 0, 1, 2, 3, 4, 5, -1
+DTYPE = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32, torch.int8: I8,
+         torch.int32: I32, torch.int64: I64}
+
+EXPORTS = (
+    "b200q_version", "b200q_last_error", "b200q_status_string", "b200q_device_error",
+    "b200q_dynamic_quant", "b200q_quant_matmul_workspace_bytes", "b200q_quant_matmul",
+    "b200q_weight_quant_matmul_workspace_bytes", "b200q_weight_quant_matmul", "b200q_int4pack",
+    "b200q_trans_quant_param",
+)
+
+
+class QuantMatmulArgs(C.Structure):
+    _fields_ = [
+        ("x1", C.c_void_p), ("x2", C.c_void_p),
+        ("m", C.c_int64), ("k", C.c_int64), ("n", C.c_int64),
+        ("x2_stride_k", C.c_int64), ("x2_stride_n", C.c_int64),
+        ("scale", C.c_void_p), ("scale_dtype", C.c_int), ("scale_len", C.c_int64),
+        ("offset", C.c_void_p), ("offset_len", C.c_int64),
+        ("pertoken_scale", C.c_void_p),
+        ("bias", C.c_void_p), ("bias_dtype", C.c_int),
+        ("out", C.c_void_p), ("out_dtype", C.c_int),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class WeightQuantMatmulArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("x_dtype", C.c_int),
+        ("weight", C.c_void_p), ("weight_bits", C.c_int),
+        ("m", C.c_int64), ("k", C.c_int64), ("n", C.c_int64),
+        ("w_stride_k", C.c_int64), ("w_stride_n", C.c_int64),
+        ("antiquant_scale", C.c_void_p), ("antiquant_offset", C.c_void_p),
+        ("group_size", C.c_int64),
+        ("bias", C.c_void_p),
+        ("out", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class B200QError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"b200q status {status}: {message}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads ``lib/libb200q.so`` (raises if it has not been built)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise ImportError(f"{_LIB_PATH} is missing: run `python -m pytorch_b200._build` "
+                              "(there is no fallback implementation)")
+        l = C.CDLL(_LIB_PATH)
+        l.b200q_version.restype = C.c_int
+        l.b200q_last_error.restype = C.c_char_p
+        l.b200q_status_string.restype = C.c_char_p
+        l.b200q_status_string.argtypes = [C.c_int]
+        l.b200q_device_error.argtypes = [C.POINTER(C.c_uint), C.c_int]
+        l.b200q_dynamic_quant.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
+                                          C.c_int64, C.c_int64, C.c_void_p]
+        l.b200q_quant_matmul_workspace_bytes.restype = C.c_size_t
+        l.b200q_quant_matmul_workspace_bytes.argtypes = [C.c_int64] * 5
+        l.b200q_quant_matmul.argtypes = [C.POINTER(QuantMatmulArgs), C.c_void_p]
+        l.b200q_weight_quant_matmul_workspace_bytes.restype = C.c_size_t
+        l.b200q_weight_quant_matmul_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.c_int]
+        l.b200q_weight_quant_matmul.argtypes = [C.POINTER(WeightQuantMatmulArgs), C.c_void_p]
+        l.b200q_int4pack.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+        l.b200q_trans_quant_param.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p]
+        _lib = l
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise B200QError(status, lib().b200q_last_error().decode() or
+                         lib().b200q_status_string(status).decode())
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise B200QError(ERR_BAD_ARG, "tensors must live on a CUDA device (there is no CPU path)")
+
+
+def device_error(reset: bool = True) -> int:
+    code = C.c_uint(0)
+    lib().b200q_device_error(C.byref(code), int(reset))
+    return code.value
+
+
+def dynamic_quant(x: torch.Tensor, smooth_scales: torch.Tensor | None = None):
+    _need_cuda(x, smooth_scales)
+    x = x.contiguous()
+    k = x.shape[-1]
+    rows = x.numel() // k if k else (x.numel() if x.dim() == 0 else int(torch.Size(x.shape[:-1]).numel()))
+    y = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    scale = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    sm = None if smooth_scales is None else smooth_scales.contiguous()
+    check(lib().b200q_dynamic_quant(_ptr(x), DTYPE[x.dtype], _ptr(sm), NONE if sm is None else DTYPE[sm.dtype],
+                                    _ptr(y), _ptr(scale), rows, k, _stream()))
+    return y, scale
+
+
+def quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None, output_dtype=None,
+                 workspace: torch.Tensor | None = None, out: torch.Tensor | None = None):
+    """2-D ``x2`` only (any strides); leading dimensions of ``x1`` are folded into m."""
+    _need_cuda(x1, x2, scale, offset, pertoken_scale, bias)
+    out_dtype = torch.int8 if output_dtype is None else output_dtype
+    x1c = x1.contiguous()
+    k, n = x2.shape
+    m = x1c.numel() // k if k else int(torch.Size(x1c.shape[:-1]).numel())
+    if out is None:
+        out = torch.empty((*x1c.shape[:-1], n), dtype=out_dtype, device=x1.device)
+    need = lib().b200q_quant_matmul_workspace_bytes(m, k, n, x2.stride(0), x2.stride(1))
+    if workspace is None and need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x1.device)
+    a = QuantMatmulArgs()
+    a.x1, a.x2 = x1c.data_ptr(), x2.data_ptr()
+    a.m, a.k, a.n = m, k, n
+    a.x2_stride_k, a.x2_stride_n = x2.stride(0), x2.stride(1)
+    sc = scale.contiguous()
+    a.scale, a.scale_dtype, a.scale_len = sc.data_ptr(), DTYPE.get(sc.dtype, 99), sc.numel()
+    keep = [sc]
+    if offset is not None:
+        of = offset.contiguous(); keep.append(of)
+        a.offset, a.offset_len = of.data_ptr(), of.numel()
+    if pertoken_scale is not None:
+        pt = pertoken_scale.contiguous(); keep.append(pt)
+        a.pertoken_scale = pt.data_ptr()
+    a.bias_dtype = NONE
+    if bias is not None:
+        b = bias.contiguous(); keep.append(b)
+        a.bias, a.bias_dtype = b.data_ptr(), DTYPE.get(b.dtype, 99)
+    a.out, a.out_dtype = out.data_ptr(), DTYPE.get(out_dtype, 99)
+    if workspace is not None:
+        a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
+    check(lib().b200q_quant_matmul(C.byref(a), _stream()))
+    return out
+
+
+def weight_quant_matmul(x, weight, antiquant_scale, antiquant_offset=None, *, bias=None,
+                        antiquant_group_size=0, workspace=None):
+    _need_cuda(x, weight, antiquant_scale, antiquant_offset, bias)
+    xc = x.contiguous()
+    k = xc.shape[-1]
+    m = xc.numel() // k
+    a = WeightQuantMatmulArgs()
+    if weight.dtype == torch.int32:
+        w = weight.contiguous()
+        n = w.shape[-1] * 8
+        a.weight_bits, a.w_stride_k, a.w_stride_n = 4, 0, 0
+    else:
+        w = weight
+        n = w.shape[-1]
+        a.weight_bits, a.w_stride_k, a.w_stride_n = 8, w.stride(0), w.stride(1)
+    out = torch.empty((*xc.shape[:-1], n), dtype=x.dtype, device=x.device)
+    sc = antiquant_scale.contiguous()
+    of = None if antiquant_offset is None else antiquant_offset.contiguous()
+    b = None if bias is None else bias.contiguous()
+    need = lib().b200q_weight_quant_matmul_workspace_bytes(m, k, n, a.weight_bits)
+    if workspace is None and need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    a.x, a.x_dtype, a.weight = xc.data_ptr(), DTYPE.get(x.dtype, 99), w.data_ptr()
+    a.m, a.k, a.n = m, k, n
+    a.antiquant_scale = sc.data_ptr()
+    a.antiquant_offset = None if of is None else of.data_ptr()
+    a.group_size = antiquant_group_size
+    a.bias = None if b is None else b.data_ptr()
+    a.out = out.data_ptr()
+    if workspace is not None:
+        a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
+    check(lib().b200q_weight_quant_matmul(C.byref(a), _stream()))
+    return out
+
+
+def int4pack(w: torch.Tensor) -> torch.Tensor:
+    _need_cuda(w)
+    wc = w.contiguous()
+    cols = wc.shape[-1]
+    rows = wc.numel() // cols if cols else 0
+    if cols % 8:
+        raise B200QError(ERR_BAD_ARG, f"int4pack: last dimension ({cols}) must be a multiple of 8")
+    out = torch.empty((*wc.shape[:-1], cols // 8), dtype=torch.int32, device=w.device)
+    check(lib().b200q_int4pack(_ptr(wc), _ptr(out), rows, cols, _stream()))
+    return out
+
+
+def trans_quant_param(scale: torch.Tensor, out_shape) -> torch.Tensor:
+    _need_cuda(scale)
+    sc = scale.contiguous().to(torch.float32)
+    out = torch.empty(tuple(out_shape), dtype=torch.int64, device=scale.device)
+    check(lib().b200q_trans_quant_param(_ptr(sc), sc.numel(), _ptr(out), out.numel(), _stream()))
+    return out

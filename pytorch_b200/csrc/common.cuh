@@ -1,0 +1,35 @@
+// Host-side helpers shared by the C-ABI translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/b200q.h"
+
+namespace b200q {
+
+// Stores the calling thread's last error message and returns `status`.
+int fail(int status, const char* fmt, ...);
+void clear_error();
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+#define B200Q_REQUIRE(cond, status, ...)            \
+  do {                                              \
+    if (!(cond)) return ::b200q::fail((status), __VA_ARGS__); \
+  } while (0)
+
+// Call after a kernel launch: turns a launch error into B200Q_ERR_LAUNCH.
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200Q_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  return B200Q_OK;
+}
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+}  // namespace b200q

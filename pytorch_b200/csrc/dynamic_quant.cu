@@ -1,0 +1,252 @@
+// npu_dynamic_quant: per-token symmetric int8 quantisation (memory-bound row kernel).
+//
+// One CTA per row.  Every thread keeps its slice of the row in registers (ITERS
+// 128-bit loads, all issued before the first use), so x is read from HBM exactly once:
+// 2 B in + 1 B out per element.  The row maximum is a warp-shuffle reduction followed by
+// one exchange through shared memory.  Quantisation is bit-exact with
+// rint(xs / scale) under IEEE division: the fast path multiplies by 1/scale and only an
+// element that lands within 2.5e-4 of a rounding boundary (where the two could differ)
+// is redone with a true division.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace b200q {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t v);
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
+  // bf16 -> fp32 is a 16-bit shift
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream(uint2* p, uint2 v) {
+  asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+
+// Eight consecutive smooth-scale values as fp32 (the vector is re-read by every row and
+// stays in L1/L2).
+__device__ __forceinline__ void load_smooth8(const float* p, float (&s)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  s[0] = a.x, s[1] = a.y, s[2] = a.z, s[3] = a.w, s[4] = b.x, s[5] = b.y, s[6] = b.z, s[7] = b.w;
+}
+template <typename ST>
+__device__ __forceinline__ void load_smooth8(const ST* p, float (&s)[8]) {
+  const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = unpack2<ST>(w[j]);
+    s[2 * j] = f.x, s[2 * j + 1] = f.y;
+  }
+}
+
+// clamp(rint(xs / scale)) with the exact-division fallback described above.
+__device__ __forceinline__ int quantize(float xs, float scale, float inv) {
+  float r = __fmul_rn(xs, inv);
+  float t = rintf(r);
+  if (fabsf(fabsf(r - t) - 0.5f) < 2.5e-4f) t = rintf(__fdiv_rn(xs, scale));
+  return max(-128, min(127, __float2int_rn(t)));
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float m = (lane < nwarps) ? red[lane] : 0.0f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  return m;
+}
+
+// Vector path: k % 8 == 0 and 16-byte aligned rows.  Thread t owns vectors t, t+blockDim, ...
+template <typename T, typename ST, int ITERS, bool SMOOTH>
+__global__ void __launch_bounds__(ITERS == 16 ? 512 : 256) dynamic_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth,
+                                                          int8_t* __restrict__ y, float* __restrict__ scale_out,
+                                                          int k) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const int nvec = k >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * k);
+  uint4 raw[ITERS];
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    raw[i] = (v < nvec) ? ld_stream(xr + v) : make_uint4(0, 0, 0, 0);
+  }
+  float amax = 0.0f;
+  if (SMOOTH) {
+    // x*smooth is recomputed in the second pass (same fp32 product, same bits) instead of
+    // being kept: registers hold the packed 16-bit row only.
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+        float sm[8];
+        load_smooth8(smooth + v * 8, sm);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = unpack2<T>(w[j]);
+          amax = fmaxf(amax, fmaxf(fabsf(__fmul_rn(f.x, sm[2 * j])), fabsf(__fmul_rn(f.y, sm[2 * j + 1]))));
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = unpack2<T>(w[j]);
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+    }
+  }
+  amax = block_max(amax, red);
+  const float scale = __fdiv_rn(amax, 127.0f);
+  if (threadIdx.x == 0) scale_out[row] = scale;
+  const bool zero = (scale == 0.0f);
+  const float inv = zero ? 0.0f : __frcp_rn(scale);
+  uint2* yr = reinterpret_cast<uint2*>(y + row * k);
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+      int q[8];
+      float sm[8];
+      if (SMOOTH) load_smooth8(smooth + v * 8, sm);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = unpack2<T>(w[j]);
+        if (SMOOTH) {
+          f.x = __fmul_rn(f.x, sm[2 * j]);
+          f.y = __fmul_rn(f.y, sm[2 * j + 1]);
+        }
+        q[2 * j] = zero ? 0 : quantize(f.x, scale, inv);
+        q[2 * j + 1] = zero ? 0 : quantize(f.y, scale, inv);
+      }
+      uint2 o;
+      o.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((q[3] & 0xFF) << 24);
+      o.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((q[7] & 0xFF) << 24);
+      st_stream(yr + v, o);
+    }
+  }
+}
+
+// Generic path: any k, any alignment; the row is read twice (second pass from L2).
+template <typename T, typename ST, bool SMOOTH>
+__global__ void dynamic_quant_rows_generic(const T* __restrict__ x, const ST* __restrict__ smooth,
+                                           int8_t* __restrict__ y, float* __restrict__ scale_out, int64_t k) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const T* xr = x + row * k;
+  float amax = 0.0f;
+  for (int64_t c = threadIdx.x; c < k; c += blockDim.x) {
+    float f = to_f32<T>(xr[c]);
+    if (SMOOTH) f = __fmul_rn(f, to_f32<ST>(smooth[c]));
+    amax = fmaxf(amax, fabsf(f));
+  }
+  amax = block_max(amax, red);
+  const float scale = __fdiv_rn(amax, 127.0f);
+  if (threadIdx.x == 0) scale_out[row] = scale;
+  for (int64_t c = threadIdx.x; c < k; c += blockDim.x) {
+    float f = to_f32<T>(xr[c]);
+    if (SMOOTH) f = __fmul_rn(f, to_f32<ST>(smooth[c]));
+    int q = 0;
+    if (scale != 0.0f) q = max(-128, min(127, __float2int_rn(rintf(__fdiv_rn(f, scale)))));
+    y[row * k + c] = static_cast<int8_t>(q);
+  }
+}
+
+template <typename T, typename ST, bool SMOOTH>
+int launch_dq(const void* x, const void* smooth, int8_t* y, float* scale, int64_t rows, int64_t k,
+              cudaStream_t st) {
+  const T* xp = static_cast<const T*>(x);
+  const ST* sp = static_cast<const ST*>(smooth);
+  const bool vec = (k % 8 == 0) && aligned(x, 16) && aligned(y, 8) && k <= 8 * 512 * 16 &&
+                   (!SMOOTH || aligned(smooth, 16));
+  if (!vec) {
+    dynamic_quant_rows_generic<T, ST, SMOOTH><<<(unsigned)rows, 256, 0, st>>>(xp, sp, y, scale, k);
+    return check_launch("dynamic_quant (generic)");
+  }
+  const int nvec = (int)(k / 8);
+  // Keep CTAs at <= 256 threads where the row allows it: more independent loads per thread,
+  // a cheaper block reduction, eight CTAs resident per SM.
+  int iters = 1;
+  while (iters < 16 && nvec > iters * 256) iters *= 2;
+  int threads = (int)ceil_div(nvec, iters);
+  threads = (int)ceil_div(threads, 32) * 32;
+#define B200Q_DQ_CASE(I)                                                                         \
+  case I:                                                                                        \
+    dynamic_quant_rows<T, ST, I, SMOOTH><<<(unsigned)rows, threads, 0, st>>>(xp, sp, y, scale, (int)k); \
+    break;
+  switch (iters) {
+    B200Q_DQ_CASE(1)
+    B200Q_DQ_CASE(2)
+    B200Q_DQ_CASE(4)
+    B200Q_DQ_CASE(8)
+    B200Q_DQ_CASE(16)
+  }
+#undef B200Q_DQ_CASE
+  return check_launch("dynamic_quant");
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" int b200q_dynamic_quant(const void* x, int x_dtype, const void* smooth, int smooth_dtype, int8_t* y,
+                                   float* scale, int64_t rows, int64_t k, void* stream) {
+  using namespace b200q;
+  clear_error();
+  B200Q_REQUIRE(rows >= 0 && k >= 0, B200Q_ERR_BAD_ARG, "dynamic_quant: negative size");
+  B200Q_REQUIRE(x_dtype == B200Q_BF16 || x_dtype == B200Q_F16, B200Q_ERR_UNSUPPORTED,
+                "dynamic_quant: input must be bf16 or f16 (dtype enum %d)", x_dtype);
+  if (rows == 0) return B200Q_OK;
+  B200Q_REQUIRE(rows <= 0x7fffffffLL, B200Q_ERR_UNSUPPORTED, "dynamic_quant: more than 2^31-1 rows");
+  B200Q_REQUIRE(scale != nullptr, B200Q_ERR_BAD_ARG, "dynamic_quant: scale is NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (k == 0) {
+    cudaError_t e = cudaMemsetAsync(scale, 0, rows * sizeof(float), st);
+    return e == cudaSuccess ? B200Q_OK : fail(B200Q_ERR_LAUNCH, "dynamic_quant: %s", cudaGetErrorString(e));
+  }
+  B200Q_REQUIRE(x != nullptr && y != nullptr, B200Q_ERR_BAD_ARG, "dynamic_quant: x or y is NULL");
+  B200Q_REQUIRE(aligned(x, 2) && aligned(scale, 4), B200Q_ERR_BAD_ARG, "dynamic_quant: misaligned buffer");
+  if (smooth == nullptr) {
+    if (x_dtype == B200Q_BF16) return launch_dq<__nv_bfloat16, float, false>(x, nullptr, y, scale, rows, k, st);
+    return launch_dq<__half, float, false>(x, nullptr, y, scale, rows, k, st);
+  }
+  B200Q_REQUIRE(smooth_dtype == B200Q_F32 || smooth_dtype == x_dtype, B200Q_ERR_UNSUPPORTED,
+                "dynamic_quant: smooth_scales must be f32 or the input's dtype");
+  if (x_dtype == B200Q_BF16) {
+    if (smooth_dtype == B200Q_F32) return launch_dq<__nv_bfloat16, float, true>(x, smooth, y, scale, rows, k, st);
+    return launch_dq<__nv_bfloat16, __nv_bfloat16, true>(x, smooth, y, scale, rows, k, st);
+  }
+  if (smooth_dtype == B200Q_F32) return launch_dq<__half, float, true>(x, smooth, y, scale, rows, k, st);
+  return launch_dq<__half, __half, true>(x, smooth, y, scale, rows, k, st);
+}

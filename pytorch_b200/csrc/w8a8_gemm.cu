@@ -1,0 +1,620 @@
+// npu_quant_matmul: int8 x int8 -> int32 GEMM on tcgen05 (kind::i8) with a fused
+// dequantisation epilogue.
+//
+// Both operands are consumed K-major (x1 [M,K]; the weight as [N,K], which is the memory
+// the reference's modules hand over as a transposed view).  One persistent CTA per SM:
+//   warp 0      TMA producer: 128x128-byte operand tiles, 128B swizzle, STAGES-deep ring
+//   warp 1      MMA issuer: tcgen05.mma.cta_group::1.kind::i8, M=128, N=BN, K=32 per instruction,
+//               accumulators in TMEM, two accumulator buffers so the epilogue of one tile
+//               overlaps the main loop of the next
+//   warps 2-5   epilogue: tcgen05.ld -> registers -> float(acc+bias)*scale*pertoken+offset -> store
+// Two operand assignments share the kernel:
+//   normal (M > 128)  A = x1 rows (tokens), B = weight rows (channels)
+//   swapped (M <= 128) A = weight rows, B = x1 rows padded to BN in {16,32,64,128}: the weight, which
+//               dominates the traffic, fills the 128-row MMA axis; K is split across CTAs so
+//               that every SM streams weights, partial sums meet in an int32 scratch through
+//               integer atomics (exact in any order) and a small kernel applies the epilogue.
+// Every mbarrier wait is bounded; on a timeout the CTA records an error code and winds down.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tensormap.cuh"
+
+namespace b200q {
+namespace {
+
+constexpr int kBK = 128;            // K bytes per pipeline stage = one 128B swizzle row
+constexpr int kTileA = 128;         // rows of the A operand per tile = UMMA M
+constexpr int kATileBytes = kTileA * kBK;
+constexpr int kEpiThreads = 128;
+constexpr int kThreads = 64 + kEpiThreads;
+
+enum EpiFlags : uint32_t {
+  kHasPt = 1, kHasOff = 2, kHasIntBias = 4, kHasFloatBias = 8,
+  kOutVec = 16   // rows of `out` are 16-byte aligned: a thread may store 128-bit vectors
+};
+
+struct Epi {
+  const void* scale;
+  const float* offset;
+  const float* pertoken;
+  const void* bias;
+  void* out;
+  int32_t* acc_ws;  // split-K: raw accumulators are added here instead of writing `out`
+  int64_t m, n;
+  int scale_dtype, scale_bcast, offset_bcast, bias_dtype, out_dtype;
+  uint32_t flags;
+};
+
+struct Sched {
+  int tiles_a, tiles_b, splits, kblocks, kb_per_split, units;
+};
+
+__device__ __forceinline__ float load_scale(const Epi& e, int64_t n) {
+  const int64_t i = e.scale_bcast ? 0 : n;
+  if (e.scale_dtype == B200Q_F32) return __ldg(static_cast<const float*>(e.scale) + i);
+  if (e.scale_dtype == B200Q_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(e.scale)[i]);
+  return __uint_as_float(static_cast<uint32_t>(static_cast<const unsigned long long*>(e.scale)[i]));
+}
+__device__ __forceinline__ float load_offset(const Epi& e, int64_t n) {
+  return (e.flags & kHasOff) ? __ldg(e.offset + (e.offset_bcast ? 0 : n)) : 0.0f;
+}
+__device__ __forceinline__ int load_int_bias(const Epi& e, int64_t n) {
+  return (e.flags & kHasIntBias) ? __ldg(static_cast<const int*>(e.bias) + n) : 0;
+}
+__device__ __forceinline__ float load_float_bias(const Epi& e, int64_t n) {
+  if (!(e.flags & kHasFloatBias)) return 0.0f;
+  if (e.bias_dtype == B200Q_F32) return __ldg(static_cast<const float*>(e.bias) + n);
+  if (e.bias_dtype == B200Q_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(e.bias)[n]);
+  return __half2float(static_cast<const __half*>(e.bias)[n]);
+}
+
+// One rounding per step, no fused multiply-add: the CPU oracle does the same five operations.
+__device__ __forceinline__ float dequant(int acc, int ib, float sc, float pt, float fb, float off, uint32_t flags) {
+  float v = __int2float_rn(acc + ib);
+  v = __fmul_rn(v, sc);
+  if (flags & kHasPt) v = __fmul_rn(v, pt);
+  if (flags & kHasFloatBias) v = __fadd_rn(v, fb);
+  if (flags & kHasOff) v = __fadd_rn(v, off);
+  return v;
+}
+
+__device__ __forceinline__ uint32_t to_bits16(float v, int out_dtype) {
+  if (out_dtype == B200Q_BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  return __half_as_ushort(__float2half_rn(v));
+}
+__device__ __forceinline__ int to_int8(float v) { return max(-128, min(127, __float2int_rn(v))); }
+
+// Stores one finished element.
+__device__ __forceinline__ void store_one(const Epi& e, int64_t idx, int acc, int ib, float v) {
+  switch (e.out_dtype) {
+    case B200Q_I32: static_cast<int*>(e.out)[idx] = acc + ib; break;
+    case B200Q_I8: static_cast<int8_t*>(e.out)[idx] = (int8_t)to_int8(v); break;
+    default: static_cast<unsigned short*>(e.out)[idx] = (unsigned short)to_bits16(v, e.out_dtype); break;
+  }
+}
+
+template <int N>
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[N]);
+template <>
+__device__ __forceinline__ void tmem_ld_chunk<32>(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld_x32(taddr, r); }
+template <>
+__device__ __forceinline__ void tmem_ld_chunk<16>(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_x16(taddr, r); }
+
+// AND-reduction of a predicate over the epilogue warps (named barrier 2).  Every epilogue
+// thread calls it once per tile, so the decision to stop is taken by all of them together.
+__device__ __forceinline__ bool epilogue_all(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 2, %2, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred), "r"(kEpiThreads)
+      : "memory");
+  return r != 0;
+}
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int kBTileBytes = BN * kBK;
+  static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+  static constexpr int kTiles = STAGES * kStageBytes;
+  static constexpr int kBarOff = kTiles;                       // full[S], empty[S], tfull[2], tempty[2]
+  static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;   // tmem base, abort flag
+  static constexpr int kColOff = kMiscOff + 16;                // 4 x BN 32-bit column parameters
+  static constexpr int kTotal = kColOff + 4 * BN * 4;
+  static constexpr int kDynamic = kTotal + 1024;               // slack to align the tiles to 1024 B
+};
+
+template <int BN, int STAGES, bool SWAP>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Epi e,
+                 const Sched s) {
+  using L = SmemLayout<BN, STAGES>;
+  constexpr int CH = BN < 32 ? 16 : 32;                 // accumulator columns per tcgen05.ld
+  constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns: power of two <= 512");
+  static_assert(kTmemCols <= 256 || L::kDynamic > 116 * 1024, "two resident CTAs must not both want >256 TMEM columns");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * kATileBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
+  float* col_f0 = reinterpret_cast<float*>(smem + L::kColOff);   // normal: scale[n]   swapped: pertoken[m]
+  float* col_f1 = col_f0 + BN;                                     // normal: offset[n]
+  float* col_f2 = col_f1 + BN;                                     // normal: float bias[n]
+  int* col_i = reinterpret_cast<int*>(col_f2 + BN);                // normal: int bias[n]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], kEpiThreads / 32);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < s.units && ok; u += gridDim.x) {
+        const int ta = u % s.tiles_a, rest = u / s.tiles_a;
+        const int tb = rest % s.tiles_b, sp = rest / s.tiles_b;
+        const int kb0 = sp * s.kb_per_split, kb1 = min(s.kblocks, kb0 + s.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, kDevTimeoutProducer)) { ok = false; break; }
+          mbar_arrive_expect_tx(&full[stage], L::kStageBytes);
+          tma_load_2d(sA + stage * kATileBytes, &tmA, &full[stage], kb * kBK, ta * kTileA);
+          tma_load_2d(sB + stage * L::kBTileBytes, &tmB, &full[stage], kb * kBK, tb * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Give copies that are still in flight time to land before shared memory is released.
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(2 /*s32*/, 1 /*s8*/, 1 /*s8*/, 0, 0, kTileA, BN);
+      int stage = 0, buf = 0;
+      uint32_t phase = 0, tphase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < s.units && ok; u += gridDim.x) {
+        const int sp = (u / s.tiles_a) / s.tiles_b;
+        const int kb0 = sp * s.kb_per_split, kb1 = min(s.kblocks, kb0 + s.kb_per_split);
+        if (!mbar_wait(&tempty[buf], tphase ^ 1, abort_flag, kDevTimeoutMma)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, kDevTimeoutMma)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc(smem_u32(sA + stage * kATileBytes), 16, 1024, kSwizzle128B);
+          const uint64_t bdesc = make_smem_desc(smem_u32(sB + stage * L::kBTileBytes), 16, 1024, kSwizzle128B);
+#pragma unroll
+          for (int k4 = 0; k4 < kBK / 32; ++k4)   // +32 bytes along K inside the swizzle row = +2 in the address field
+            umma_i8(d_tmem, adesc + 2 * k4, bdesc + 2 * k4, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+          umma_commit(&empty[stage]);             // stage is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[buf]);                 // accumulator complete
+        if (++buf == 2) { buf = 0; tphase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int et = threadIdx.x - 64;                 // 0..127
+    const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    int buf = 0;
+    uint32_t tphase = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < s.units && ok; u += gridDim.x) {
+      const int ta = u % s.tiles_a, tb = (u / s.tiles_a) % s.tiles_b;
+      // Column parameters of this tile -> shared memory (read back as broadcasts).
+      named_barrier_sync(1, kEpiThreads);
+      if (SWAP) {
+        for (int i = et; i < BN; i += kEpiThreads) {
+          const int64_t mm = (int64_t)tb * BN + i;
+          col_f0[i] = ((e.flags & kHasPt) && mm < e.m) ? __ldg(e.pertoken + mm) : 1.0f;
+        }
+      } else {
+        for (int i = et; i < BN; i += kEpiThreads) {
+          const int64_t nn = (int64_t)tb * BN + i;
+          const bool v = nn < e.n;
+          col_f0[i] = v ? load_scale(e, nn) : 0.0f;
+          col_f1[i] = v ? load_offset(e, nn) : 0.0f;
+          col_f2[i] = v ? load_float_bias(e, nn) : 0.0f;
+          col_i[i] = v ? load_int_bias(e, nn) : 0;
+        }
+      }
+      named_barrier_sync(1, kEpiThreads);
+
+      if (!epilogue_all(mbar_wait(&tfull[buf], tphase, abort_flag, kDevTimeoutEpilogue))) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
+
+      if (SWAP) {
+        // D rows are channels (n), D columns are tokens (m): lanes write consecutive n.
+        const int64_t n = (int64_t)ta * kTileA + row_in_tile;
+        const bool nv = n < e.n;
+        const float sc = nv ? load_scale(e, n) : 0.0f, off = nv ? load_offset(e, n) : 0.0f;
+        const float fb = nv ? load_float_bias(e, n) : 0.0f;
+        const int ib = nv ? load_int_bias(e, n) : 0;
+#pragma unroll 1
+        for (int c = 0; c < BN / CH; ++c) {
+          uint32_t r[CH];
+          __syncwarp();
+          tmem_ld_chunk<CH>(taddr + c * CH, r);
+          tmem_ld_wait();
+          if (nv) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int64_t mm = (int64_t)tb * BN + c * CH + j;
+              if (mm < e.m) {
+                const int acc = (int)r[j];
+                if (e.acc_ws) {
+                  atomicAdd(e.acc_ws + mm * e.n + n, acc);
+                } else {
+                  store_one(e, mm * e.n + n, acc, ib, dequant(acc, ib, sc, col_f0[c * CH + j], fb, off, e.flags));
+                }
+              }
+            }
+          }
+        }
+      } else {
+        // D rows are tokens (m), D columns are channels (n): a thread owns CH consecutive n of one row.
+        const int64_t mm = (int64_t)ta * kTileA + row_in_tile;
+        const bool mv = mm < e.m;
+        const float pt = (mv && (e.flags & kHasPt)) ? __ldg(e.pertoken + mm) : 1.0f;
+        const bool vec = (e.flags & kOutVec) != 0;
+#pragma unroll 1
+        for (int c = 0; c < BN / CH; ++c) {
+          uint32_t r[CH];
+          __syncwarp();
+          tmem_ld_chunk<CH>(taddr + c * CH, r);
+          tmem_ld_wait();
+          const int64_t n0 = (int64_t)tb * BN + c * CH;
+          if (!mv || n0 >= e.n) continue;
+          if (e.acc_ws) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j)
+              if (n0 + j < e.n) atomicAdd(e.acc_ws + mm * e.n + n0 + j, (int)r[j]);
+          } else if (vec && n0 + CH <= e.n) {
+            // The thread's CH results are contiguous in the output row: 128-bit stores.
+            if (e.out_dtype == B200Q_I32) {
+              uint4* dst = reinterpret_cast<uint4*>(static_cast<int*>(e.out) + mm * e.n + n0);
+#pragma unroll
+              for (int q = 0; q < CH / 4; ++q)
+                dst[q] = make_uint4(r[4 * q] + col_i[c * CH + 4 * q], r[4 * q + 1] + col_i[c * CH + 4 * q + 1],
+                                    r[4 * q + 2] + col_i[c * CH + 4 * q + 2], r[4 * q + 3] + col_i[c * CH + 4 * q + 3]);
+            } else if (e.out_dtype == B200Q_I8) {
+              uint32_t packed[CH / 4];
+#pragma unroll
+              for (int j = 0; j < CH; j += 4) {
+                uint32_t w = 0;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                  const int cj = c * CH + j + b;
+                  const float v = dequant((int)r[j + b], col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags);
+                  w |= (uint32_t)(to_int8(v) & 0xFF) << (8 * b);
+                }
+                packed[j / 4] = w;
+              }
+              uint4* dst = reinterpret_cast<uint4*>(static_cast<int8_t*>(e.out) + mm * e.n + n0);
+#pragma unroll
+              for (int q = 0; q < CH / 16; ++q)
+                dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            } else {
+              uint32_t packed[CH / 2];
+#pragma unroll
+              for (int j = 0; j < CH; j += 2) {
+                const int cj = c * CH + j;
+                const float v0 = dequant((int)r[j], col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags);
+                const float v1 =
+                    dequant((int)r[j + 1], col_i[cj + 1], col_f0[cj + 1], pt, col_f2[cj + 1], col_f1[cj + 1], e.flags);
+                packed[j / 2] = to_bits16(v0, e.out_dtype) | (to_bits16(v1, e.out_dtype) << 16);
+              }
+              uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned short*>(e.out) + mm * e.n + n0);
+#pragma unroll
+              for (int q = 0; q < CH / 8; ++q)
+                dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              if (n0 + j < e.n) {
+                const int cj = c * CH + j;
+                const int acc = (int)r[j];
+                store_one(e, mm * e.n + n0 + j, acc, col_i[cj],
+                          dequant(acc, col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags));
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[buf]);
+      if (++buf == 2) { buf = 0; tphase ^= 1; }
+    }
+  }
+
+  // Teardown: every role arrives here whether it finished or aborted.
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Applies the epilogue to split-K accumulators: one thread per output element.
+__global__ void splitk_finalize_kernel(const int32_t* __restrict__ acc, const Epi e) {
+  const int64_t total = e.m * e.n;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t mm = i / e.n, n = i - mm * e.n;
+    const int a = acc[i], ib = load_int_bias(e, n);
+    const float pt = (e.flags & kHasPt) ? __ldg(e.pertoken + mm) : 1.0f;
+    store_one(e, i, a, ib, dequant(a, ib, load_scale(e, n), pt, load_float_bias(e, n), load_offset(e, n), e.flags));
+  }
+}
+
+// Any shape, any strides: one thread per output element.  Used for operands that do not meet
+// the TMA alignment rules (K not a multiple of 16, odd pointers) and for K == 0.
+__global__ void w8a8_simt_kernel(const int8_t* __restrict__ x1, const int8_t* __restrict__ x2, int64_t k,
+                                 int64_t sk, int64_t sn, const Epi e) {
+  const int64_t n = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  const int64_t mm = blockIdx.y * (int64_t)blockDim.y + threadIdx.y;
+  if (n >= e.n || mm >= e.m) return;
+  int acc = 0;
+  const int8_t* a = x1 + mm * k;
+  const int8_t* b = x2 + n * sn;
+  for (int64_t i = 0; i < k; ++i) acc += (int)a[i] * (int)b[i * sk];
+  const int ib = load_int_bias(e, n);
+  const float pt = (e.flags & kHasPt) ? __ldg(e.pertoken + mm) : 1.0f;
+  store_one(e, mm * e.n + n, acc, ib,
+            dequant(acc, ib, load_scale(e, n), pt, load_float_bias(e, n), load_offset(e, n), e.flags));
+}
+
+// int8 [k,n] row-major -> [n,k] row-major through a 64x64 shared tile (k, n multiples of 16).
+__global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t* __restrict__ src, int8_t* __restrict__ dst,
+                                                          int64_t k, int64_t n) {
+  __shared__ __align__(16) uint8_t tile[64][80];
+  const int64_t k0 = (int64_t)blockIdx.y * 64, n0 = (int64_t)blockIdx.x * 64;
+  const int r = threadIdx.x >> 2, seg = threadIdx.x & 3;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (k0 + r < k && n0 + seg * 16 < n) v = *reinterpret_cast<const uint4*>(src + (k0 + r) * n + n0 + seg * 16);
+  *reinterpret_cast<uint4*>(&tile[r][seg * 16]) = v;
+  __syncthreads();
+  if (n0 + r < n && k0 + seg * 16 < k) {
+    uint32_t w[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t x = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) x |= (uint32_t)tile[seg * 16 + q * 4 + b][r] << (8 * b);
+      w[q] = x;
+    }
+    *reinterpret_cast<uint4*>(dst + (n0 + r) * k + k0 + seg * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+template <int BN, int STAGES, bool SWAP>
+int launch_umma(const CUtensorMap& tmA, const CUtensorMap& tmB, const Epi& e, const Sched& s, cudaStream_t st) {
+  using L = SmemLayout<BN, STAGES>;
+  static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
+  auto kern = w8a8_umma_kernel<BN, STAGES, SWAP>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (err != cudaSuccess) return fail(B200Q_ERR_LAUNCH, "quant_matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(err));
+    configured[dev] = true;
+  }
+  const int grid = s.units < sm_count() ? s.units : sm_count();
+  kern<<<grid, kThreads, L::kDynamic, st>>>(tmA, tmB, e, s);
+  return check_launch("quant_matmul (tcgen05)");
+}
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+// Layout decision shared by the workspace query and the launch.
+struct Plan {
+  bool tensor_path;     // tcgen05 path usable
+  bool transpose;       // contiguous [k,n] weight must be re-laid out as [n,k] first
+  bool swap;            // M <= 128
+  int bn;               // B-operand tile rows
+  int splits;
+  size_t ws_transpose, ws_acc;
+};
+
+Plan make_plan(int64_t m, int64_t k, int64_t n, int64_t sk, int64_t sn, const void* x1, const void* x2) {
+  Plan p{};
+  const bool kmajor = (sk == 1 || k == 1) && (sn >= k) && (sn % 16 == 0);
+  const bool nmajor = (sn == 1 || n == 1) && (sk == n) && (n % 16 == 0);
+  p.tensor_path = k >= 16 && k % 16 == 0 && (kmajor || nmajor) && m > 0 && n > 0 &&
+                  (x1 == nullptr || aligned(x1, 16)) && (x2 == nullptr || aligned(x2, 16)) &&
+                  k <= (1LL << 31) && m < (1LL << 31) && n < (1LL << 31);
+  if (!p.tensor_path) return p;
+  p.transpose = !kmajor;
+  p.ws_transpose = p.transpose ? align256((size_t)n * k) : 0;
+  p.swap = m <= 128;
+  p.splits = 1;
+  if (p.swap) {
+    p.bn = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
+    // Split K so that all SMs stream weights; cost = (weight bytes + atomic traffic) / SM utilisation.
+    const int sms = sm_count();
+    const int64_t tiles = ceil_div(n, kTileA), kblocks = ceil_div(k, kBK);
+    double best = 1e300;
+    for (int sp = 1; sp <= 32 && sp <= kblocks; ++sp) {
+      const int64_t per = ceil_div(kblocks, sp), eff_sp = ceil_div(kblocks, per);
+      if (eff_sp != sp) continue;
+      const int64_t units = tiles * sp;
+      const double util = (double)units / (double)(ceil_div(units, sms) * sms);
+      const double bytes = (double)k * n + (sp > 1 ? (double)sp * m * n * 8.0 : 0.0);
+      const double cost = bytes / util;
+      if (cost < best * 0.98) { best = cost; p.splits = sp; }
+    }
+    p.ws_acc = p.splits > 1 ? align256((size_t)m * n * 4) : 0;
+  } else {
+    p.bn = n <= 128 ? 128 : 256;
+  }
+  return p;
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" size_t b200q_quant_matmul_workspace_bytes(int64_t m, int64_t k, int64_t n, int64_t x2_stride_k,
+                                                     int64_t x2_stride_n) {
+  using namespace b200q;
+  if (m <= 0 || k <= 0 || n <= 0) return 0;
+  Plan p = make_plan(m, k, n, x2_stride_k, x2_stride_n, nullptr, nullptr);
+  return p.tensor_path ? p.ws_transpose + p.ws_acc : 0;
+}
+
+extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream) {
+  using namespace b200q;
+  clear_error();
+  B200Q_REQUIRE(a != nullptr, B200Q_ERR_BAD_ARG, "quant_matmul: args is NULL");
+  B200Q_REQUIRE(a->m >= 0 && a->k >= 0 && a->n >= 0, B200Q_ERR_BAD_ARG, "quant_matmul: negative size");
+  if (a->m == 0 || a->n == 0) return B200Q_OK;
+  B200Q_REQUIRE(a->out != nullptr && a->scale != nullptr, B200Q_ERR_BAD_ARG, "quant_matmul: out or scale is NULL");
+  B200Q_REQUIRE(a->k == 0 || (a->x1 != nullptr && a->x2 != nullptr), B200Q_ERR_BAD_ARG, "quant_matmul: x1 or x2 is NULL");
+  B200Q_REQUIRE(a->out_dtype == B200Q_I8 || a->out_dtype == B200Q_F16 || a->out_dtype == B200Q_BF16 ||
+                    a->out_dtype == B200Q_I32,
+                B200Q_ERR_UNSUPPORTED, "quant_matmul: output dtype enum %d is not int8/f16/bf16/int32", a->out_dtype);
+  B200Q_REQUIRE(a->scale_dtype == B200Q_F32 || a->scale_dtype == B200Q_BF16 || a->scale_dtype == B200Q_I64,
+                B200Q_ERR_UNSUPPORTED, "quant_matmul: scale must be f32, bf16 or i64 (dtype enum %d)", a->scale_dtype);
+  B200Q_REQUIRE(a->scale_len == 1 || a->scale_len == a->n, B200Q_ERR_BAD_ARG,
+                "quant_matmul: scale has %lld elements, expected 1 or n=%lld", (long long)a->scale_len, (long long)a->n);
+  B200Q_REQUIRE(a->offset == nullptr || a->offset_len == 1 || a->offset_len == a->n, B200Q_ERR_BAD_ARG,
+                "quant_matmul: offset has %lld elements, expected 1 or n=%lld", (long long)a->offset_len, (long long)a->n);
+  B200Q_REQUIRE(a->bias == nullptr || a->bias_dtype == B200Q_I32 || a->bias_dtype == B200Q_BF16 ||
+                    a->bias_dtype == B200Q_F16 || a->bias_dtype == B200Q_F32,
+                B200Q_ERR_UNSUPPORTED, "quant_matmul: bias must be i32, bf16, f16 or f32");
+  B200Q_REQUIRE(!(a->out_dtype == B200Q_I32 && a->bias != nullptr && a->bias_dtype != B200Q_I32), B200Q_ERR_UNSUPPORTED,
+                "quant_matmul: int32 output takes an int32 bias only");
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Epi e{};
+  e.scale = a->scale; e.offset = a->offset; e.pertoken = a->pertoken_scale; e.bias = a->bias; e.out = a->out;
+  e.acc_ws = nullptr; e.m = a->m; e.n = a->n;
+  e.scale_dtype = a->scale_dtype; e.scale_bcast = a->scale_len == 1; e.offset_bcast = a->offset_len == 1;
+  e.bias_dtype = a->bias ? a->bias_dtype : B200Q_NONE; e.out_dtype = a->out_dtype;
+  e.flags = (a->pertoken_scale ? kHasPt : 0u) | (a->offset ? kHasOff : 0u) |
+            (a->bias ? (a->bias_dtype == B200Q_I32 ? kHasIntBias : kHasFloatBias) : 0u);
+  {
+    const int64_t ob = a->out_dtype == B200Q_I8 ? 1 : a->out_dtype == B200Q_I32 ? 4 : 2;
+    if (aligned(a->out, 16) && (a->n * ob) % 16 == 0) e.flags |= kOutVec;
+  }
+
+  Plan p = make_plan(a->m, a->k, a->n, a->x2_stride_k, a->x2_stride_n, a->x1, a->x2);
+  if (!p.tensor_path) {
+    dim3 block(32, 8), grid((unsigned)ceil_div(a->n, 32), (unsigned)ceil_div(a->m, 8));
+    B200Q_REQUIRE(grid.y <= 65535, B200Q_ERR_UNSUPPORTED,
+                  "quant_matmul: operands that miss the 16-byte alignment rules are limited to m <= 524280");
+    w8a8_simt_kernel<<<grid, block, 0, st>>>(a->x1, a->x2, a->k, a->x2_stride_k, a->x2_stride_n, e);
+    return check_launch("quant_matmul (simt)");
+  }
+  const size_t need = p.ws_transpose + p.ws_acc;
+  B200Q_REQUIRE(need == 0 || (a->workspace != nullptr && a->workspace_bytes >= need && aligned(a->workspace, 256)),
+                B200Q_ERR_WORKSPACE, "quant_matmul: needs %zu bytes of 256-byte aligned workspace, got %zu", need,
+                a->workspace_bytes);
+
+  const int8_t* w_nk = a->x2;
+  int64_t w_pitch = a->x2_stride_n;
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  if (p.transpose) {
+    int8_t* wt = reinterpret_cast<int8_t*>(ws);
+    dim3 grid((unsigned)ceil_div(a->n, 64), (unsigned)ceil_div(a->k, 64));
+    transpose_i8_kernel<<<grid, 256, 0, st>>>(a->x2, wt, a->k, a->n);
+    if (int rc = check_launch("quant_matmul (weight re-layout)")) return rc;
+    w_nk = wt;
+    w_pitch = a->k;
+  }
+  if (p.ws_acc) {
+    e.acc_ws = reinterpret_cast<int32_t*>(ws + p.ws_transpose);
+    cudaError_t err = cudaMemsetAsync(e.acc_ws, 0, (size_t)a->m * a->n * 4, st);
+    if (err != cudaSuccess) return fail(B200Q_ERR_LAUNCH, "quant_matmul: memset: %s", cudaGetErrorString(err));
+  }
+
+  // A operand fills the 128-row MMA axis: tokens normally, channels when swapped.
+  const int8_t* a_ptr = p.swap ? w_nk : a->x1;
+  const int64_t a_rows = p.swap ? a->n : a->m, a_pitch = p.swap ? w_pitch : a->k;
+  const int8_t* b_ptr = p.swap ? a->x1 : w_nk;
+  const int64_t b_rows = p.swap ? a->m : a->n, b_pitch = p.swap ? a->k : w_pitch;
+  CUtensorMap tmA, tmB;
+  if (int rc = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_ptr, a->k, a_rows, a_pitch, kBK, kTileA,
+                            CU_TENSOR_MAP_SWIZZLE_128B, "quant_matmul (A operand)"))
+    return rc;
+  if (int rc = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_ptr, a->k, b_rows, b_pitch, kBK, p.bn,
+                            CU_TENSOR_MAP_SWIZZLE_128B, "quant_matmul (B operand)"))
+    return rc;
+
+  Sched s{};
+  s.tiles_a = (int)ceil_div(a_rows, kTileA);
+  s.tiles_b = (int)ceil_div(b_rows, p.bn);
+  s.kblocks = (int)ceil_div(a->k, kBK);
+  s.kb_per_split = (int)ceil_div(s.kblocks, p.splits);
+  s.splits = (int)ceil_div(s.kblocks, s.kb_per_split);
+  const int64_t units = (int64_t)s.tiles_a * s.tiles_b * s.splits;
+  B200Q_REQUIRE(units < (1LL << 31), B200Q_ERR_UNSUPPORTED, "quant_matmul: too many tiles");
+  s.units = (int)units;
+
+  int rc;
+  if (p.swap) {
+    switch (p.bn) {
+      case 16: rc = launch_umma<16, 8, true>(tmA, tmB, e, s, st); break;
+      case 32: rc = launch_umma<32, 8, true>(tmA, tmB, e, s, st); break;
+      case 64: rc = launch_umma<64, 8, true>(tmA, tmB, e, s, st); break;
+      default: rc = launch_umma<128, 6, true>(tmA, tmB, e, s, st); break;
+    }
+  } else {
+    rc = (p.bn == 128) ? launch_umma<128, 6, false>(tmA, tmB, e, s, st) : launch_umma<256, 4, false>(tmA, tmB, e, s, st);
+  }
+  if (rc) return rc;
+  if (e.acc_ws) {
+    Epi f = e;
+    f.acc_ws = nullptr;
+    const int64_t total = a->m * a->n;
+    const int blocks = (int)(ceil_div(total, 256) < (int64_t)sm_count() * 8 ? ceil_div(total, 256) : (int64_t)sm_count() * 8);
+    splitk_finalize_kernel<<<blocks, 256, 0, st>>>(e.acc_ws, f);
+    return check_launch("quant_matmul (split-K epilogue)");
+  }
+  return B200Q_OK;
+}
