@@ -1,0 +1,64 @@
+"""Column-sharded (N-sharded) W8A8 linear across the GPUs of one node.
+
+The reference's own sharding rule for a matmul is ``(Replicate, Shard(last)) -> Shard(last)``
+(``torch_npu/distributed/tensor/_matrix_ops.py:143-146``) with the per-channel scales following
+their operand (``:495-500``): rank r of g holds rows ``[r*N/g, (r+1)*N/g)`` of the ``[N,K]``
+weight and the matching slice of ``scale`` / ``offset`` / ``bias``; activations, smooth scales
+and the per-token scale are replicated.  The only exchange step is an all-gather of the
+``[M, N/g]`` outputs along N, which the reference issues as ``hcclAllGather``
+(``torch_npu/csrc/distributed/ProcessGroupHCCL.cpp:5896-5956``) and which runs here as
+``ncclAllGather`` over NVLink through ``torch.distributed``.  With a world size of one no
+collective is issued.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n: int, rank: int, world: int) -> tuple[int, int]:
+    """Half-open column range of ``rank``; ``n`` must divide evenly."""
+    if n % world:
+        raise ValueError(f"n={n} is not divisible by the world size {world}")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_weight(weight_nk: torch.Tensor, *per_channel: torch.Tensor | None, rank: int, world: int):
+    """Cuts an ``[N,K]`` weight and its per-channel vectors (``[N]``) for ``rank``."""
+    lo, hi = shard_bounds(weight_nk.shape[0], rank, world)
+    return (weight_nk[lo:hi].contiguous(),
+            *[None if p is None else (p if p.numel() == 1 else p[lo:hi].contiguous()) for p in per_channel])
+
+
+class ColumnShardedOutput:
+    """Reusable buffers for gathering ``[M, N/g]`` shards into ``[M, N]``.
+
+    ``all_gather_into_tensor`` delivers ``[g, M, N/g]`` (rank-major); one strided copy
+    re-interleaves the column blocks into the row-major ``[M, N]`` the caller expects."""
+
+    def __init__(self, m: int, n: int, dtype: torch.dtype, device, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.m, self.n = m, n
+        if self.world > 1:
+            self.staging = torch.empty((self.world, m, n // self.world), dtype=dtype, device=device)
+            self.full = torch.empty((m, n), dtype=dtype, device=device)
+
+    def gather(self, shard: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return shard
+        dist.all_gather_into_tensor(self.staging, shard.contiguous(), group=self.group)
+        self.full.view(self.m, self.world, self.n // self.world).copy_(self.staging.permute(1, 0, 2))
+        return self.full
+
+
+def sharded_w8a8_linear(x: torch.Tensor, smooth_scales, weight_nk_shard: torch.Tensor, scale_shard: torch.Tensor,
+                        gather: ColumnShardedOutput, *, output_dtype=torch.bfloat16, quantized=None):
+    """dynamic quant (replicated) -> W8A8 GEMM on this rank's columns -> all-gather along N.
+
+    ``quantized`` may carry the ``(int8, scale)`` pair of an earlier call on the same ``x``."""
+    ops = torch.ops.npu
+    q, s = quantized if quantized is not None else ops.npu_dynamic_quant(x, smooth_scales=smooth_scales)
+    y = ops.npu_quant_matmul(q, weight_nk_shard.t(), scale_shard, pertoken_scale=s, output_dtype=output_dtype)
+    return gather.gather(y)
