@@ -4,8 +4,8 @@
 // 128-bit loads, all issued before the first use), so x is read from HBM exactly once:
 // 2 B in + 1 B out per element.  The row maximum is a warp-shuffle reduction followed by
 // one exchange through shared memory.  Quantisation is bit-exact with
-// rint(xs / scale) under IEEE division: the fast path multiplies by 1/scale and only an
-// element that lands within 2.5e-4 of a rounding boundary (where the two could differ)
+// rint(xs / scale) under IEEE division: the fast path multiplies by 1/scale and only a
+// vector with an element within 2.5e-4 of a rounding boundary (where the two could differ)
 // is redone with a true division.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -63,12 +63,31 @@ __device__ __forceinline__ void load_smooth8(const ST* p, float (&s)[8]) {
   }
 }
 
-// clamp(rint(xs / scale)) with the exact-division fallback described above.
-__device__ __forceinline__ int quantize(float xs, float scale, float inv) {
-  float r = __fmul_rn(xs, inv);
-  float t = rintf(r);
-  if (fabsf(fabsf(r - t) - 0.5f) < 2.5e-4f) t = rintf(__fdiv_rn(xs, scale));
-  return max(-128, min(127, __float2int_rn(t)));
+// Eight values -> eight int8 (packed), bit-exact with clamp(rint(xs / scale)).
+// Fast path: r = xs * (1/scale); adding 1.5 * 2^23 rounds r to the nearest-even integer and leaves
+// its two's-complement low byte in the low mantissa byte (|r| <= 127.0001 because scale = amax/127, so
+// no clamp is needed).  r can differ from the true quotient by a few 1e-5, so the two can only round
+// differently when r is within 2.5e-4 of a half-integer: such a vector is redone with IEEE division.
+__device__ __forceinline__ uint2 quantize8(const float (&f)[8], float scale, float inv) {
+  constexpr float kMagic = 12582912.0f;
+  uint32_t u[8];
+  bool slow = false;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float r = __fmul_rn(f[j], inv);
+    const float uf = __fadd_rn(r, kMagic);
+    const float t = __fsub_rn(uf, kMagic);
+    slow |= fabsf(__fsub_rn(r, t)) > 0.49975f;
+    u[j] = __float_as_uint(uf);
+  }
+  if (slow) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) u[j] = (uint32_t)__float2int_rn(__fdiv_rn(f[j], scale));
+  }
+  uint2 o;
+  o.x = __byte_perm(__byte_perm(u[0], u[1], 0x0040), __byte_perm(u[2], u[3], 0x0040), 0x5410);
+  o.y = __byte_perm(__byte_perm(u[4], u[5], 0x0040), __byte_perm(u[6], u[7], 0x0040), 0x5410);
+  return o;
 }
 
 __device__ __forceinline__ float block_max(float v, float* red) {
@@ -130,30 +149,22 @@ __global__ void __launch_bounds__(ITERS == 16 ? 512 : 256) dynamic_quant_rows(co
   amax = block_max(amax, red);
   const float scale = __fdiv_rn(amax, 127.0f);
   if (threadIdx.x == 0) scale_out[row] = scale;
-  const bool zero = (scale == 0.0f);
-  const float inv = zero ? 0.0f : __frcp_rn(scale);
+  const float inv = (scale == 0.0f) ? 0.0f : __frcp_rn(scale);   // all-zero row: every product is 0
   uint2* yr = reinterpret_cast<uint2*>(y + row * k);
 #pragma unroll
   for (int i = 0; i < ITERS; ++i) {
     const int v = threadIdx.x + i * blockDim.x;
     if (v < nvec) {
       const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-      int q[8];
-      float sm[8];
+      float f[8], sm[8];
       if (SMOOTH) load_smooth8(smooth + v * 8, sm);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        float2 f = unpack2<T>(w[j]);
-        if (SMOOTH) {
-          f.x = __fmul_rn(f.x, sm[2 * j]);
-          f.y = __fmul_rn(f.y, sm[2 * j + 1]);
-        }
-        q[2 * j] = zero ? 0 : quantize(f.x, scale, inv);
-        q[2 * j + 1] = zero ? 0 : quantize(f.y, scale, inv);
+        const float2 p = unpack2<T>(w[j]);
+        f[2 * j] = SMOOTH ? __fmul_rn(p.x, sm[2 * j]) : p.x;
+        f[2 * j + 1] = SMOOTH ? __fmul_rn(p.y, sm[2 * j + 1]) : p.y;
       }
-      uint2 o;
-      o.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((q[3] & 0xFF) << 24);
-      o.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((q[7] & 0xFF) << 24);
+      const uint2 o = quantize8(f, scale, inv);
       st_stream(yr + v, o);
     }
   }
