@@ -186,44 +186,48 @@ def unpack_int4(p: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------- A3
 def dequant_weight(weight, antiquant_scale, antiquant_offset=None, antiquant_group_size=0,
                    dequant_dtype=None):
-    """fp32 ``(w + offset) * scale`` of an int8 ``[K,N]`` or int4-packed int32
-    ``[K,N/8]`` weight.  Scale/offset are per channel (``[N]`` / ``[1,N]``) or per
-    group of ``antiquant_group_size`` rows of K (``[K/gs, N]``).  ``dequant_dtype``
-    (fp16/bf16) rounds the sum and the product to that type, which is what the
-    reference's golden does when it is handed fp16 tensors
-    (``test/contrib/test_linear_weight_quant.py:21-26``); the default keeps fp32."""
+    """``(w + offset) * scale`` of an int8 ``[K,N]`` or int4-packed int32 ``[K,N/8]`` weight, returned
+    as fp32.  Scale/offset are per channel (``[N]`` / ``[1,N]``) or per group of
+    ``antiquant_group_size`` rows of K (``[K/gs, N]``).
+
+    ``dequant_dtype`` is the type the two steps are carried out in.  The reference's golden for the
+    weight-only matmul works on the tensors it is given, i.e. in fp16/bf16: the sum ``w + offset`` is
+    rounded to that type, then the product with ``scale`` is rounded again, and only then is the
+    result widened for the fp32 matmul (``test/contrib/test_linear_weight_quant.py:21-26``).  Passing
+    the activation dtype reproduces that; ``None`` keeps both steps in fp32 (the order used by
+    ``test/custom_ops/test_npu_anti_quant.py:36-41``)."""
     w = unpack_int4(weight) if weight.dtype == torch.int32 else weight.detach().cpu()
-    if dequant_dtype is not None:
-        k, n = w.shape[-2], w.shape[-1]
-        wl = w.to(dequant_dtype)
-        if antiquant_offset is not None:
-            wl = wl + antiquant_offset.detach().cpu().to(dequant_dtype).reshape(-1, n)
-        wl = wl * antiquant_scale.detach().cpu().to(dequant_dtype).reshape(-1, n)
-        return wl.to(torch.float32).numpy()
-    w = w.to(torch.float32).numpy()
     k, n = w.shape[-2], w.shape[-1]
 
-    def expand(p):
-        a = _to_f32(p)
-        if a.ndim == 2 and a.shape[0] > 1:
+    def expand(p, dt):
+        a = p.detach().cpu().to(dt)
+        if a.dim() == 2 and a.shape[0] > 1:
             gs = antiquant_group_size if antiquant_group_size > 0 else k // a.shape[0]
-            a = np.repeat(a, gs, axis=0)[:k]
-        return a.reshape(-1, n) if a.ndim <= 2 else a
+            a = a.repeat_interleave(gs, dim=0)[:k]
+        return a.reshape(-1, n)
 
+    dt = torch.float32 if dequant_dtype is None else dequant_dtype
+    wl = w.to(dt)
     if antiquant_offset is not None:
-        w = w + expand(antiquant_offset)
-    return (w * expand(antiquant_scale)).astype(F32)
+        wl = wl + expand(antiquant_offset, dt)
+    wl = wl * expand(antiquant_scale, dt)
+    return wl.to(torch.float32).numpy()
 
 
 def weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset=None,
                              quant_scale=None, quant_offset=None, bias=None,
-                             antiquant_group_size=0, inner_precise=0, dequant_dtype=None):
-    """``npu_weight_quant_batchmatmul``: ``x @ ((w + offset) * scale) (+ bias)``,
-    result in ``x.dtype`` (``test/contrib/test_linear_weight_quant.py:20-28``).
-    The product is accumulated in float64 and rounded once to fp32 so that the
-    value does not depend on the host's summation order."""
+                             antiquant_group_size=0, inner_precise=0, dequant_dtype="x"):
+    """``npu_weight_quant_batchmatmul``: ``x @ ((w + offset) * scale) (+ bias)``, result in ``x.dtype``.
+
+    Follows the reference's golden, ``test/contrib/test_linear_weight_quant.py:20-28``: the weight is
+    dequantised in the activation dtype (``dequant_dtype="x"``, see ``dequant_weight``), widened to
+    fp32, multiplied and cast.  The product is accumulated in float64 and rounded once to fp32 so
+    that the value does not depend on the host's summation order.  ``dequant_dtype=None`` gives the
+    all-fp32 dequantisation instead."""
     if quant_scale is not None or quant_offset is not None or inner_precise != 0:
         raise NotImplementedError("requantised output / inner_precise are outside the path")
+    if isinstance(dequant_dtype, str):
+        dequant_dtype = x.dtype
     wd = dequant_weight(weight, antiquant_scale, antiquant_offset, antiquant_group_size, dequant_dtype)
     xf = x.detach().cpu().to(torch.float64)
     out = torch.matmul(xf, torch.from_numpy(wd).to(torch.float64)).to(torch.float32).numpy()

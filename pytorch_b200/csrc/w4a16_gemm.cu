@@ -14,8 +14,8 @@
 //                in TMEM; tcgen05.commit frees the stage
 // After the last K block the dequantising warps turn into the epilogue: tcgen05.ld, bias,
 // cast, coalesced stores along n.  int4 values are expanded with the exponent-bias trick
-// (nibble placed in the mantissa of 128.0 / 1024.0, then one subtract and one fused multiply-add
-// per pair); int8 values go through fp32, in the oracle's own order of operations.
+// (nibble placed in the mantissa of 128.0 / 1024.0, then one exact subtract); w + offset and the
+// product with scale are packed 16-bit operations, rounded exactly as the reference's golden does.
 // All mbarrier waits are bounded (see ptx.cuh).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -73,13 +73,25 @@ struct X2<__half> {
   }
 };
 
+// The dequantisation repeats the reference golden's arithmetic in the activation dtype
+// (test/contrib/test_linear_weight_quant.py:21-26): w + offset rounded to 16 bits, then the product
+// with scale rounded again.  Integer weights are exact in fp16 and bf16.
 template <typename XT>
-__device__ __forceinline__ uint32_t sub_fma2(uint32_t t, uint32_t sc, uint32_t os) {
+__device__ __forceinline__ uint32_t add_mul2(uint32_t w2, uint32_t of2, uint32_t sc2, bool has_offset) {
+  using V = typename X2<XT>::type;
+  V w = *reinterpret_cast<const V*>(&w2);
+  if (has_offset) w = __hadd2(w, *reinterpret_cast<const V*>(&of2));
+  V r = __hmul2(w, *reinterpret_cast<const V*>(&sc2));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+// Two int4 values sitting in bits [0,4) and [16,20) of t -> exact 16-bit floats (exponent-bias trick).
+template <typename XT>
+__device__ __forceinline__ uint32_t nibbles_to_x2(uint32_t t) {
   using V = typename X2<XT>::type;
   const uint32_t magic = X2<XT>::kMagic;
-  V w = __hsub2(*reinterpret_cast<const V*>(&t), *reinterpret_cast<const V*>(&magic));
-  V r = __hfma2(w, *reinterpret_cast<const V*>(&sc), *reinterpret_cast<const V*>(&os));
-  return *reinterpret_cast<uint32_t*>(&r);
+  const uint32_t biased = (t & 0x000F000Fu) ^ magic;
+  V w = __hsub2(*reinterpret_cast<const V*>(&biased), *reinterpret_cast<const V*>(&magic));
+  return *reinterpret_cast<uint32_t*>(&w);
 }
 
 template <int LAYOUT, int BNX>
@@ -242,8 +254,9 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       const int64_t n_tile0 = (int64_t)tn * kWqTileN;
       int64_t cur_group = -1;
       // Per-thread dequantisation parameters (refreshed when the K block enters a new group).
-      uint32_t sc2[4], os2[4];                         // kW4N: packed pairs (j, j+4)
-      float scf[8], off[8];                            // kW8N: this thread's 8 channels; kW8K: 4 rows in [0..3]
+      // 16-bit pairs: kW4N (j, j+4) of this thread's 8 channels; kW8N (2j, 2j+1); kW8K row i twice.
+      uint32_t sc2[4], of2[4];
+      const bool has_off = p.offset != nullptr;
       for (int kb = 0; kb < p.kblocks; ++kb) {
         const int64_t g = p.group_size > 0 ? ((int64_t)kb * kWqBK) / p.group_size : 0;
         if (g != cur_group) {
@@ -253,17 +266,19 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             for (int i = 0; i < 4; ++i) {
               const int64_t n = n_tile0 + (t >> 3) + 32 * i;
               const bool v = n < p.n;
-              scf[i] = v ? X2<XT>::to_float(static_cast<const XT*>(p.scale)[g * p.n + n]) : 0.0f;
-              off[i] = (v && p.offset) ? X2<XT>::to_float(static_cast<const XT*>(p.offset)[g * p.n + n]) : 0.0f;
+              const float sc = v ? X2<XT>::to_float(static_cast<const XT*>(p.scale)[g * p.n + n]) : 0.0f;
+              const float of = (v && has_off) ? X2<XT>::to_float(static_cast<const XT*>(p.offset)[g * p.n + n]) : 0.0f;
+              sc2[i] = X2<XT>::pack(sc, sc);
+              of2[i] = X2<XT>::pack(of, of);
             }
           } else {
+            float scf[8], off[8];
             load_params8<XT>(p, g, n_tile0 + (t & 15) * 8, scf, off);
-            if (LAYOUT == kW4N) {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                sc2[j] = X2<XT>::pack(scf[j], scf[j + 4]);
-                os2[j] = X2<XT>::pack(__fmul_rn(off[j], scf[j]), __fmul_rn(off[j + 4], scf[j + 4]));
-              }
+            for (int j = 0; j < 4; ++j) {
+              const int a = LAYOUT == kW4N ? j : 2 * j, b = LAYOUT == kW4N ? j + 4 : 2 * j + 1;
+              sc2[j] = X2<XT>::pack(scf[a], scf[b]);     // values are 16-bit already: packing is exact
+              of2[j] = X2<XT>::pack(off[a], off[b]);
             }
           }
         }
@@ -281,10 +296,8 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const uint32_t v = reinterpret_cast<const uint32_t*>(raw)[kr * 16 + wc];
             uint32_t pr[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t tb = ((v >> (4 * j)) & 0x000F000Fu) ^ X2<XT>::kMagic;   // halves: values j and j+4
-              pr[j] = sub_fma2<XT>(tb, sc2[j], os2[j]);
-            }
+            for (int j = 0; j < 4; ++j)                  // halves: values j and j+4
+              pr[j] = add_mul2<XT>(nibbles_to_x2<XT>(v >> (4 * j)), of2[j], sc2[j], has_off);
             uint4 o;
             o.x = __byte_perm(pr[0], pr[1], 0x5410);   // (v0, v1)
             o.y = __byte_perm(pr[2], pr[3], 0x5410);   // (v2, v3)
@@ -306,7 +319,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             for (int j = 0; j < 8; j += 2) {
               const float a = (float)(int8_t)(w2[j >> 2] >> (8 * (j & 3)));
               const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
-              o[j >> 1] = X2<XT>::pack(__fmul_rn(__fadd_rn(a, off[j]), scf[j]), __fmul_rn(__fadd_rn(b, off[j + 1]), scf[j + 1]));
+              o[j >> 1] = add_mul2<XT>(X2<XT>::pack(a, b), of2[j >> 1], sc2[j >> 1], has_off);
             }
             const uint32_t r = kr & 7;
             *reinterpret_cast<uint4*>(a_tile + ng * 8192 + (kr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
@@ -324,7 +337,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             for (int j = 0; j < 8; j += 2) {
               const float a = (float)(int8_t)(w2[j >> 2] >> (8 * (j & 3)));
               const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
-              o[j >> 1] = X2<XT>::pack(__fmul_rn(__fadd_rn(a, off[i]), scf[i]), __fmul_rn(__fadd_rn(b, off[i]), scf[i]));
+              o[j >> 1] = add_mul2<XT>(X2<XT>::pack(a, b), of2[i], sc2[i], has_off);
             }
             const uint32_t r = nr & 7;
             *reinterpret_cast<uint4*>(a_tile + (nr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
@@ -414,7 +427,10 @@ __global__ void wq_simt_kernel(const XT* __restrict__ x, const void* __restrict_
     }
     const float sc = X2<XT>::to_float(static_cast<const XT*>(p.scale)[g * p.n + n]);
     const float of = p.offset ? X2<XT>::to_float(static_cast<const XT*>(p.offset)[g * p.n + n]) : 0.0f;
-    acc = fmaf(X2<XT>::to_float(x[mm * p.k + kk]), __fmul_rn(__fadd_rn(wv, of), sc), acc);
+    float wd = wv;                                    // two roundings in the activation dtype, as above
+    if (p.offset) wd = X2<XT>::to_float(X2<XT>::from_float(__fadd_rn(wd, of)));
+    wd = X2<XT>::to_float(X2<XT>::from_float(__fmul_rn(wd, sc)));
+    acc = fmaf(X2<XT>::to_float(x[mm * p.k + kk]), wd, acc);
   }
   if (p.bias) acc += X2<XT>::to_float(static_cast<const XT*>(p.bias)[n]);
   static_cast<XT*>(p.out)[mm * p.n + n] = X2<XT>::from_float(acc);

@@ -53,16 +53,16 @@ def test_antiquant_matches_reference_golden(ref):
 
 def test_weight_quant_matmul_matches_reference_golden(ref):
     # The reference golden is handed fp16 tensors, so it rounds (w+offset) and the product
-    # to fp16 before its fp32 matmul.  With the same dequant precision the oracle must agree
-    # to fp16 rounding of the result (fp32 vs fp64 summation); with fp32 dequant (what the
-    # oracle uses for parity) the difference is the golden's own fp16 rounding of the weights.
+    # to fp16 before its fp32 matmul.  The oracle's default does the same and must agree to
+    # fp16 rounding of the result (fp32 vs fp64 summation); with an all-fp32 dequantisation the
+    # difference is the golden's own fp16 rounding of the weights.
     args = (torch.from_numpy(ref["wq_x"]), torch.from_numpy(ref["wq_w_nk"]).t(),
             torch.from_numpy(ref["wq_scale"]), torch.from_numpy(ref["wq_offset"]))
     want = torch.from_numpy(ref["wq_out"])
-    got16 = oracle.weight_quant_batchmatmul(*args, dequant_dtype=torch.float16)
+    got16 = oracle.weight_quant_batchmatmul(*args)
     assert got16.dtype == torch.float16
     assert oracle.max_mixed_error(got16, want) <= 2 ** -10
-    got = oracle.weight_quant_batchmatmul(*args)
+    got = oracle.weight_quant_batchmatmul(*args, dequant_dtype=None)
     assert oracle.max_mixed_error(got, want) <= 2 ** -5
 
 
