@@ -89,6 +89,27 @@ size_t b200q_quant_matmul_workspace_bytes(int64_t m, int64_t k, int64_t n, int64
                                           int64_t x2_stride_n);
 int b200q_quant_matmul(const b200q_quant_matmul_args* args, void* stream);
 
+/* b200q_quant_matmul for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: its operators always draw workspace from the framework's allocator.)
+ *   Who needs it: a host that cannot call cudaMalloc or torch's allocator when the matmul runs, e.g. a
+ *   server that has already given all free HBM to its KV-cache pool, a plugin living inside another
+ *   runtime's fixed memory plan, or a code path where an allocation, which may synchronise the device,
+ *   is not allowed.  Such a caller has nothing to put into args->workspace.
+ *   What it does: same arguments, same kernels and bit-identical results as b200q_quant_matmul, but
+ *   args->workspace / workspace_bytes are ignored and the scratch (split-K accumulators, weight
+ *   re-layout) comes from an array of b200q_static_scratch_bytes() = 16 MiB built into the library.
+ *   Every GPU that loads the library holds that array until the process exits.  It calls no
+ *   cudaMalloc/cudaFree and no allocating library routine.
+ *   Limit: shapes whose b200q_quant_matmul_workspace_bytes() exceeds 16 MiB are refused with
+ *   B200Q_ERR_WORKSPACE (nothing is launched); use b200q_quant_matmul for those.
+ *   First call on a device: looks up the array's device address (cudaGetSymbolAddress, once per device,
+ *   cached).  Make that first call before starting any stream capture.
+ *   Sharing: all calls on a device use the same array and it keeps its last contents; the part that
+ *   must start at zero is cleared on `stream` inside every call.  Two calls that overlap on the GPU
+ *   (different streams without an ordering between them) race on the array: serialise them. */
+size_t b200q_static_scratch_bytes(void);
+int b200q_quant_matmul_static_scratch(const b200q_quant_matmul_args* args, void* stream);
+
 /* npu_weight_quant_batchmatmul(x, weight, antiquant_scale, antiquant_offset, ..., antiquant_group_size)
  *   replaces op_plugin::npu_weight_quant_batchmatmul / aclnnWeightQuantBatchMatmulV2, reached from
  *   torch_npu/contrib/module/linear_weight_quant.py:106-109.

@@ -23,6 +23,7 @@ DTYPE = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32, torch.int
 EXPORTS = (
     "b200q_version", "b200q_last_error", "b200q_status_string", "b200q_device_error",
     "b200q_dynamic_quant", "b200q_quant_matmul_workspace_bytes", "b200q_quant_matmul",
+    "b200q_static_scratch_bytes", "b200q_quant_matmul_static_scratch",
     "b200q_weight_quant_matmul_workspace_bytes", "b200q_weight_quant_matmul", "b200q_int4pack",
     "b200q_trans_quant_param",
 )
@@ -83,6 +84,8 @@ def lib() -> C.CDLL:
         l.b200q_quant_matmul_workspace_bytes.restype = C.c_size_t
         l.b200q_quant_matmul_workspace_bytes.argtypes = [C.c_int64] * 5
         l.b200q_quant_matmul.argtypes = [C.POINTER(QuantMatmulArgs), C.c_void_p]
+        l.b200q_static_scratch_bytes.restype = C.c_size_t
+        l.b200q_quant_matmul_static_scratch.argtypes = [C.POINTER(QuantMatmulArgs), C.c_void_p]
         l.b200q_weight_quant_matmul_workspace_bytes.restype = C.c_size_t
         l.b200q_weight_quant_matmul_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int64, C.c_int]
         l.b200q_weight_quant_matmul.argtypes = [C.POINTER(WeightQuantMatmulArgs), C.c_void_p]
@@ -132,8 +135,13 @@ def dynamic_quant(x: torch.Tensor, smooth_scales: torch.Tensor | None = None):
 
 
 def quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None, output_dtype=None,
-                 workspace: torch.Tensor | None = None, out: torch.Tensor | None = None):
-    """2-D ``x2`` only (any strides); leading dimensions of ``x1`` are folded into m."""
+                 workspace: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                 static_scratch: bool = False):
+    """2-D ``x2`` only (any strides); leading dimensions of ``x1`` are folded into m.
+
+    ``static_scratch=True`` goes through ``b200q_quant_matmul_static_scratch``: no workspace is
+    allocated or passed; the library's built-in scratch array is used instead (``out`` should then be
+    supplied by a caller that truly cannot allocate)."""
     _need_cuda(x1, x2, scale, offset, pertoken_scale, bias)
     out_dtype = torch.int8 if output_dtype is None else output_dtype
     x1c = x1.contiguous()
@@ -142,7 +150,7 @@ def quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None, 
     if out is None:
         out = torch.empty((*x1c.shape[:-1], n), dtype=out_dtype, device=x1.device)
     need = lib().b200q_quant_matmul_workspace_bytes(m, k, n, x2.stride(0), x2.stride(1))
-    if workspace is None and need:
+    if workspace is None and need and not static_scratch:
         workspace = torch.empty(need, dtype=torch.uint8, device=x1.device)
     a = QuantMatmulArgs()
     a.x1, a.x2 = x1c.data_ptr(), x2.data_ptr()
@@ -162,6 +170,9 @@ def quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None, 
         b = bias.contiguous(); keep.append(b)
         a.bias, a.bias_dtype = b.data_ptr(), DTYPE.get(b.dtype, 99)
     a.out, a.out_dtype = out.data_ptr(), DTYPE.get(out_dtype, 99)
+    if static_scratch:
+        check(lib().b200q_quant_matmul_static_scratch(C.byref(a), _stream()))
+        return out
     if workspace is not None:
         a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
     check(lib().b200q_quant_matmul(C.byref(a), _stream()))

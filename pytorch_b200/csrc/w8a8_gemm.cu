@@ -18,6 +18,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tensormap.cuh"
@@ -617,4 +619,71 @@ extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream
     return check_launch("quant_matmul (split-K epilogue)");
   }
   return B200Q_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Entry point for callers that cannot allocate device memory.
+//
+// Some hosts of this library never get to call cudaMalloc (or torch's allocator) at the moment a
+// matmul is needed: an inference server that has already handed all free device memory to its
+// KV-cache pool, a plugin that runs inside another framework's memory plan, code on a path where
+// an allocation (which may synchronise the device) is forbidden.  b200q_quant_matmul asks such a
+// caller for workspace it has no way to provide.  This variant takes the scratch for the split-K
+// accumulators and for the [k,n] -> [n,k] weight re-layout from a fixed array that lives in the
+// library's device image instead; every GPU that loads the library holds those 16 MiB until the
+// process exits.
+namespace b200q {
+namespace {
+
+constexpr size_t kStaticScratchBytes = size_t(16) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle for the runtime, not a device address; the address
+// is looked up once per device (with that device current) and cached.
+int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* cached[64] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64)
+    return fail(B200Q_ERR_LAUNCH, "quant_matmul_static_scratch: no current CUDA device (%s)",
+                e != cudaSuccess ? cudaGetErrorString(e) : "device index out of range");
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(B200Q_ERR_LAUNCH, "quant_matmul_static_scratch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    cached[dev] = p;
+  }
+  *out = cached[dev];
+  return B200Q_OK;
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" size_t b200q_static_scratch_bytes(void) { return b200q::kStaticScratchBytes; }
+
+extern "C" int b200q_quant_matmul_static_scratch(const b200q_quant_matmul_args* a, void* stream) {
+  using namespace b200q;
+  clear_error();
+  B200Q_REQUIRE(a != nullptr, B200Q_ERR_BAD_ARG, "quant_matmul_static_scratch: args is NULL");
+  const size_t need = b200q_quant_matmul_workspace_bytes(a->m, a->k, a->n, a->x2_stride_k, a->x2_stride_n);
+  B200Q_REQUIRE(need <= kStaticScratchBytes, B200Q_ERR_WORKSPACE,
+                "quant_matmul_static_scratch: this shape needs %zu bytes of scratch, the built-in array holds %zu; "
+                "use b200q_quant_matmul with caller-provided workspace",
+                need, kStaticScratchBytes);
+  b200q_quant_matmul_args with_scratch = *a;
+  with_scratch.workspace = nullptr;
+  with_scratch.workspace_bytes = 0;
+  if (need != 0) {
+    void* scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    with_scratch.workspace = scratch;
+    with_scratch.workspace_bytes = kStaticScratchBytes;
+  }
+  // The accumulator region is cleared on the stream by the matmul itself before every use, so
+  // whatever an earlier call left in the array cannot leak into this one.
+  return b200q_quant_matmul(&with_scratch, stream);
 }
