@@ -1,7 +1,8 @@
 // npu_dynamic_quant: per-token symmetric int8 quantisation (memory-bound row kernel).
 //
-// One CTA per row.  Every thread keeps its slice of the row in registers (ITERS
-// 128-bit loads, all issued before the first use), so x is read from HBM exactly once:
+// One CTA works on one row at a time (persistent CTAs stride over the rows).  Every thread keeps
+// its slice of the row in registers (ITERS 128-bit loads, all issued before the first use, the next
+// row's loads in flight during the arithmetic), so x is read from HBM exactly once:
 // 2 B in + 1 B out per element.  The row maximum is a warp-shuffle reduction followed by
 // one exchange through shared memory.  Quantisation is bit-exact with
 // rint(xs / scale) under IEEE division: the fast path multiplies by 1/scale and only a
@@ -103,69 +104,80 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 }
 
 // Vector path: k % 8 == 0 and 16-byte aligned rows.  Thread t owns vectors t, t+blockDim, ...
-template <typename T, typename ST, int ITERS, bool SMOOTH>
-__global__ void __launch_bounds__(ITERS == 16 ? 512 : 256) dynamic_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth,
-                                                          int8_t* __restrict__ y, float* __restrict__ scale_out,
-                                                          int k) {
-  __shared__ float red[32];
-  const int64_t row = blockIdx.x;
+// Persistent CTAs walk the rows with a stride of gridDim.x; with PREFETCH the loads of the CTA's
+// next row are issued before the arithmetic of the current one, so memory latency and the
+// quantisation arithmetic overlap inside every CTA instead of relying on neighbouring CTAs.
+template <typename T, typename ST, int ITERS, bool SMOOTH, bool PREFETCH>
+__global__ void __launch_bounds__(512) dynamic_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth,
+                                                         int8_t* __restrict__ y, float* __restrict__ scale_out,
+                                                         int64_t rows, int k) {
+  __shared__ float red[2][32];
   const int nvec = k >> 3;
-  const uint4* xr = reinterpret_cast<const uint4*>(x + row * k);
-  uint4 raw[ITERS];
+  uint4 cur[ITERS], nxt[ITERS];
+  auto load_row = [&](uint4 (&dst)[ITERS], int64_t row) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * k);
 #pragma unroll
-  for (int i = 0; i < ITERS; ++i) {
-    const int v = threadIdx.x + i * blockDim.x;
-    raw[i] = (v < nvec) ? ld_stream(xr + v) : make_uint4(0, 0, 0, 0);
-  }
-  float amax = 0.0f;
-  if (SMOOTH) {
-    // x*smooth is recomputed in the second pass (same fp32 product, same bits) instead of
-    // being kept: registers hold the packed 16-bit row only.
+    for (int i = 0; i < ITERS; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      dst[i] = (v < nvec) ? ld_stream(xr + v) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  int64_t row = blockIdx.x;
+  if (row < rows) load_row(cur, row);
+  int par = 0;
+  for (; row < rows; row += gridDim.x, par ^= 1) {
+    if (PREFETCH && row + gridDim.x < rows) load_row(nxt, row + gridDim.x);
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      const uint32_t w[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+      if (SMOOTH) {
+        // x*smooth is recomputed in the second pass (same fp32 product, same bits) instead of
+        // being kept: registers hold the packed 16-bit row only.
+        if (v < nvec) {
+          float sm[8];
+          load_smooth8(smooth + v * 8, sm);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack2<T>(w[j]);
+            amax = fmaxf(amax, fmaxf(fabsf(__fmul_rn(f.x, sm[2 * j])), fabsf(__fmul_rn(f.y, sm[2 * j + 1]))));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack2<T>(w[j]);
+          amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+      }
+    }
+    amax = block_max(amax, red[par]);
+    const float scale = __fdiv_rn(amax, 127.0f);
+    if (threadIdx.x == 0) scale_out[row] = scale;
+    const float inv = (scale == 0.0f) ? 0.0f : __frcp_rn(scale);   // all-zero row: every product is 0
+    uint2* yr = reinterpret_cast<uint2*>(y + row * k);
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
       const int v = threadIdx.x + i * blockDim.x;
       if (v < nvec) {
-        const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-        float sm[8];
-        load_smooth8(smooth + v * 8, sm);
+        const uint32_t w[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
+        float f[8], sm[8];
+        if (SMOOTH) load_smooth8(smooth + v * 8, sm);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          float2 f = unpack2<T>(w[j]);
-          amax = fmaxf(amax, fmaxf(fabsf(__fmul_rn(f.x, sm[2 * j])), fabsf(__fmul_rn(f.y, sm[2 * j + 1]))));
+          const float2 pr = unpack2<T>(w[j]);
+          f[2 * j] = SMOOTH ? __fmul_rn(pr.x, sm[2 * j]) : pr.x;
+          f[2 * j + 1] = SMOOTH ? __fmul_rn(pr.y, sm[2 * j + 1]) : pr.y;
         }
+        st_stream(yr + v, quantize8(f, scale, inv));
       }
     }
-  } else {
+    if (PREFETCH) {
 #pragma unroll
-    for (int i = 0; i < ITERS; ++i) {
-      const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = unpack2<T>(w[j]);
-        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-      }
-    }
-  }
-  amax = block_max(amax, red);
-  const float scale = __fdiv_rn(amax, 127.0f);
-  if (threadIdx.x == 0) scale_out[row] = scale;
-  const float inv = (scale == 0.0f) ? 0.0f : __frcp_rn(scale);   // all-zero row: every product is 0
-  uint2* yr = reinterpret_cast<uint2*>(y + row * k);
-#pragma unroll
-  for (int i = 0; i < ITERS; ++i) {
-    const int v = threadIdx.x + i * blockDim.x;
-    if (v < nvec) {
-      const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-      float f[8], sm[8];
-      if (SMOOTH) load_smooth8(smooth + v * 8, sm);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 p = unpack2<T>(w[j]);
-        f[2 * j] = SMOOTH ? __fmul_rn(p.x, sm[2 * j]) : p.x;
-        f[2 * j + 1] = SMOOTH ? __fmul_rn(p.y, sm[2 * j + 1]) : p.y;
-      }
-      const uint2 o = quantize8(f, scale, inv);
-      st_stream(yr + v, o);
+      for (int i = 0; i < ITERS; ++i) cur[i] = nxt[i];
+    } else if (row + gridDim.x < rows) {
+      load_row(cur, row + gridDim.x);
     }
   }
 }
@@ -207,22 +219,28 @@ int launch_dq(const void* x, const void* smooth, int8_t* y, float* scale, int64_
     return check_launch("dynamic_quant (generic)");
   }
   const int nvec = (int)(k / 8);
-  // Keep CTAs at <= 256 threads where the row allows it: more independent loads per thread,
-  // a cheaper block reduction, eight CTAs resident per SM.
+  // Up to eight 128-bit loads per thread and <= 256 threads per CTA where the row allows it (k <= 16384);
+  // longer rows widen the CTA to 512 threads, and beyond k = 32768 take 16 loads without prefetch.
   int iters = 1;
-  while (iters < 16 && nvec > iters * 256) iters *= 2;
+  while (iters < 8 && nvec > iters * 256) iters *= 2;
+  if (nvec > iters * 512) iters = 16;
   int threads = (int)ceil_div(nvec, iters);
   threads = (int)ceil_div(threads, 32) * 32;
-#define B200Q_DQ_CASE(I)                                                                         \
-  case I:                                                                                        \
-    dynamic_quant_rows<T, ST, I, SMOOTH><<<(unsigned)rows, threads, 0, st>>>(xp, sp, y, scale, (int)k); \
-    break;
+  int per_sm = 1;
+#define B200Q_DQ_CASE(I, PF)                                                                                  \
+  case I: {                                                                                                    \
+    auto kern = dynamic_quant_rows<T, ST, I, SMOOTH, PF>;                                                      \
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0);                                  \
+    const int64_t cap = (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);                                       \
+    kern<<<(unsigned)(rows < cap ? rows : cap), threads, 0, st>>>(xp, sp, y, scale, rows, (int)k);            \
+    break;                                                                                                     \
+  }
   switch (iters) {
-    B200Q_DQ_CASE(1)
-    B200Q_DQ_CASE(2)
-    B200Q_DQ_CASE(4)
-    B200Q_DQ_CASE(8)
-    B200Q_DQ_CASE(16)
+    B200Q_DQ_CASE(1, true)
+    B200Q_DQ_CASE(2, true)
+    B200Q_DQ_CASE(4, true)
+    B200Q_DQ_CASE(8, true)
+    B200Q_DQ_CASE(16, false)
   }
 #undef B200Q_DQ_CASE
   return check_launch("dynamic_quant");

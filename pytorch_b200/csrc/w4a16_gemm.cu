@@ -6,7 +6,8 @@
 // packed.  Per 64-deep K block:
 //   warp 0       TMA: packed weight tile (4 KB int4 / 8 KB int8) and the activation tile
 //                [BNX tokens x 64 k] (128B swizzle) into a ring of stages
-//   warps 2-9    dequantise the packed tile in registers, (w + offset) * scale, and write it as
+//   warps 2-17   in G groups, each owning every G-th K block (so G stages are in work at once):
+//                dequantise the packed tile in registers, (w + offset) * scale, and write it as
 //                a bf16/fp16 UMMA operand tile in shared memory (canonical 128B-swizzled layout;
 //                MN-major when the weight is n-contiguous, K-major when it is k-contiguous),
 //                fence.proxy.async, signal
@@ -31,7 +32,7 @@ namespace {
 
 constexpr int kWqBK = 64;                   // K elements per stage (one 128-byte swizzle row of bf16)
 constexpr int kWqTileN = 128;               // output channels per tile = UMMA M
-constexpr int kWqDeqWarps = 8;
+constexpr int kWqDeqWarps = 16;
 constexpr int kWqDeqThreads = kWqDeqWarps * 32;
 constexpr int kWqThreads = 64 + kWqDeqThreads;
 constexpr int kWqABytes = kWqTileN * kWqBK * 2;
@@ -141,6 +142,102 @@ __device__ __forceinline__ void load_params8(const WqParams& p, int64_t g, int64
   }
 }
 
+// Dequantises one packed [64 k x 128 n] tile into the UMMA operand tile, using the GT threads of a
+// warp group (thread index lg).  Packed words are fetched in batches of eight before any arithmetic
+// so that the shared-memory latency and the dependent 16-bit operations of different items overlap.
+template <int LAYOUT, typename XT, int GT>
+__device__ __forceinline__ void dequant_tile(const uint8_t* __restrict__ raw, uint8_t* __restrict__ a_tile, int lg,
+                                             const uint32_t (&sc2)[4], const uint32_t (&of2)[4], bool has_off,
+                                             const WqParams& p, int64_t g, int64_t n_tile0) {
+  constexpr int ITEMS = (kWqBK * 16) / GT;             // 8-value items per thread (1024 per tile)
+  constexpr int BATCH = ITEMS < 8 ? ITEMS : 8;
+  if constexpr (LAYOUT == kW4N) {
+    const int wc = lg & 15;                            // 8-channel group inside the tile
+    const uint32_t ng = wc >> 3, c = wc & 7;
+    const uint32_t* raw32 = reinterpret_cast<const uint32_t*>(raw);
+#pragma unroll
+    for (int b0 = 0; b0 < ITEMS; b0 += BATCH) {
+      uint32_t v[BATCH];
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) v[i] = raw32[((lg >> 4) + (GT / 16) * (b0 + i)) * 16 + wc];
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int kr = (lg >> 4) + (GT / 16) * (b0 + i);
+        uint32_t pr[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)                    // halves of pr[j]: values j and j+4
+          pr[j] = add_mul2<XT>(nibbles_to_x2<XT>(v[i] >> (4 * j)), of2[j], sc2[j], has_off);
+        uint4 o;
+        o.x = __byte_perm(pr[0], pr[1], 0x5410);       // (v0, v1)
+        o.y = __byte_perm(pr[2], pr[3], 0x5410);       // (v2, v3)
+        o.z = __byte_perm(pr[0], pr[1], 0x7632);       // (v4, v5)
+        o.w = __byte_perm(pr[2], pr[3], 0x7632);       // (v6, v7)
+        const uint32_t r = kr & 7;
+        *reinterpret_cast<uint4*>(a_tile + ng * 8192 + (kr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) = o;
+      }
+    }
+  } else if constexpr (LAYOUT == kW8N) {
+    const int wc = lg & 15;
+    const uint32_t ng = wc >> 3, c = wc & 7;
+    const uint2* raw64 = reinterpret_cast<const uint2*>(raw);
+#pragma unroll
+    for (int b0 = 0; b0 < ITEMS; b0 += BATCH) {
+      uint2 v[BATCH];
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) v[i] = raw64[((lg >> 4) + (GT / 16) * (b0 + i)) * 16 + wc];
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int kr = (lg >> 4) + (GT / 16) * (b0 + i);
+        const uint32_t w2[2] = {v[i].x, v[i].y};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const float a = (float)(int8_t)(w2[j >> 2] >> (8 * (j & 3)));
+          const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
+          o[j >> 1] = add_mul2<XT>(X2<XT>::pack(a, b), of2[j >> 1], sc2[j >> 1], has_off);
+        }
+        const uint32_t r = kr & 7;
+        *reinterpret_cast<uint4*>(a_tile + ng * 8192 + (kr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
+            make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  } else {
+    const uint32_t c = lg & 7;                         // 8-wide k chunk inside the 64-deep block
+    const uint2* raw64 = reinterpret_cast<const uint2*>(raw);
+#pragma unroll
+    for (int b0 = 0; b0 < ITEMS; b0 += BATCH) {
+      uint2 v[BATCH];
+      uint32_t s2[BATCH], o2[BATCH];
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int nr = (lg >> 3) + (GT / 8) * (b0 + i);    // channel row inside the tile
+        const int64_t n = n_tile0 + nr;
+        const bool nv = n < p.n;
+        const float scv = nv ? X2<XT>::to_float(static_cast<const XT*>(p.scale)[g * p.n + n]) : 0.0f;
+        const float ofv = (nv && has_off) ? X2<XT>::to_float(static_cast<const XT*>(p.offset)[g * p.n + n]) : 0.0f;
+        s2[i] = X2<XT>::pack(scv, scv);
+        o2[i] = X2<XT>::pack(ofv, ofv);
+        v[i] = raw64[nr * 8 + c];
+      }
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int nr = (lg >> 3) + (GT / 8) * (b0 + i);
+        const uint32_t w2[2] = {v[i].x, v[i].y};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const float a = (float)(int8_t)(w2[j >> 2] >> (8 * (j & 3)));
+          const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
+          o[j >> 1] = add_mul2<XT>(X2<XT>::pack(a, b), o2[i], s2[i], has_off);
+        }
+        const uint32_t r = nr & 7;
+        *reinterpret_cast<uint4*>(a_tile + (nr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
+            make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+}
+
 template <int LAYOUT, typename XT, int BNX>
 __global__ void __launch_bounds__(kWqThreads, 1)
 wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const WqParams p) {
@@ -165,7 +262,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
       mbar_init(&full[i], 1);
-      mbar_init(&deq[i], kWqDeqWarps);
+      mbar_init(&deq[i], kWqDeqWarps / (STAGES >= 8 ? 8 : STAGES >= 4 ? 4 : 2));
       mbar_init(&empty[i], 1);
     }
     mbar_init(tfull, 1);
@@ -243,112 +340,51 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     }
   } else {
     // ------------------------------------------- dequantise, then epilogue
-    const int t = threadIdx.x - 64;                    // 0..255
-    const int dw = warp - 2;                           // 0..7
+    // The sixteen warps form G groups; group g owns every G-th K block, so G stages are being
+    // dequantised at the same time and no warp waits for another inside a stage.
+    constexpr int G = STAGES >= 8 ? 8 : STAGES >= 4 ? 4 : 2;
+    constexpr int WG = kWqDeqWarps / G;                // warps per group
+    constexpr int GT = WG * 32;                        // threads per group
+    const int dw = warp - 2;                           // 0..15
+    const int group = dw / WG;
+    const int lg = (dw % WG) * 32 + lane;              // thread index inside the group
     const int quad = warp & 3;                         // TMEM lane quadrant of this warp
-    int stage = 0;
-    uint32_t phase = 0, tphase = 0;
+    const bool has_off = p.offset != nullptr;
+    int it_base = 0;                                   // K blocks this CTA has been through before this tile
+    uint32_t tphase = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
       const int tn = u % p.tiles_n, mc = u / p.tiles_n;
       const int64_t n_tile0 = (int64_t)tn * kWqTileN;
       int64_t cur_group = -1;
-      // Per-thread dequantisation parameters (refreshed when the K block enters a new group).
-      // 16-bit pairs: kW4N (j, j+4) of this thread's 8 channels; kW8N (2j, 2j+1); kW8K row i twice.
-      uint32_t sc2[4], of2[4];
-      const bool has_off = p.offset != nullptr;
+      uint32_t sc2[4], of2[4];   // this thread's 8 channels as 16-bit pairs: kW4N (j, j+4), kW8N (2j, 2j+1)
       for (int kb = 0; kb < p.kblocks; ++kb) {
+        const int it = it_base + kb;
+        if ((it % G) != group) continue;
+        const int stage = it % STAGES;
+        const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
         const int64_t g = p.group_size > 0 ? ((int64_t)kb * kWqBK) / p.group_size : 0;
-        if (g != cur_group) {
+        if (LAYOUT != kW8K && g != cur_group) {
           cur_group = g;
-          if (LAYOUT == kW8K) {
+          float scf[8], off[8];
+          load_params8<XT>(p, g, n_tile0 + (lg & 15) * 8, scf, off);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int64_t n = n_tile0 + (t >> 3) + 32 * i;
-              const bool v = n < p.n;
-              const float sc = v ? X2<XT>::to_float(static_cast<const XT*>(p.scale)[g * p.n + n]) : 0.0f;
-              const float of = (v && has_off) ? X2<XT>::to_float(static_cast<const XT*>(p.offset)[g * p.n + n]) : 0.0f;
-              sc2[i] = X2<XT>::pack(sc, sc);
-              of2[i] = X2<XT>::pack(of, of);
-            }
-          } else {
-            float scf[8], off[8];
-            load_params8<XT>(p, g, n_tile0 + (t & 15) * 8, scf, off);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int a = LAYOUT == kW4N ? j : 2 * j, b = LAYOUT == kW4N ? j + 4 : 2 * j + 1;
-              sc2[j] = X2<XT>::pack(scf[a], scf[b]);     // values are 16-bit already: packing is exact
-              of2[j] = X2<XT>::pack(off[a], off[b]);
-            }
+          for (int j = 0; j < 4; ++j) {
+            const int a = LAYOUT == kW4N ? j : 2 * j, b = LAYOUT == kW4N ? j + 4 : 2 * j + 1;
+            sc2[j] = X2<XT>::pack(scf[a], scf[b]);       // values are 16-bit already: packing is exact
+            of2[j] = X2<XT>::pack(off[a], off[b]);
           }
         }
         // warp-uniform decision, so that the warp stays converged for __syncwarp below
         const bool got = __all_sync(0xffffffffu, mbar_wait(&full[stage], phase, abort_flag, kDevTimeoutEpilogue));
         if (!got) { ok = false; break; }
-        const uint8_t* raw = sRaw + stage * C::kRawBytes;
-        uint8_t* a_tile = sA + stage * kWqABytes;
-        if (LAYOUT == kW4N) {
-          const int wc = t & 15;                       // 8-channel group inside the tile
-          const uint32_t ng = wc >> 3, c = wc & 7;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int kr = (t >> 4) + 16 * i;
-            const uint32_t v = reinterpret_cast<const uint32_t*>(raw)[kr * 16 + wc];
-            uint32_t pr[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)                  // halves: values j and j+4
-              pr[j] = add_mul2<XT>(nibbles_to_x2<XT>(v >> (4 * j)), of2[j], sc2[j], has_off);
-            uint4 o;
-            o.x = __byte_perm(pr[0], pr[1], 0x5410);   // (v0, v1)
-            o.y = __byte_perm(pr[2], pr[3], 0x5410);   // (v2, v3)
-            o.z = __byte_perm(pr[0], pr[1], 0x7632);   // (v4, v5)
-            o.w = __byte_perm(pr[2], pr[3], 0x7632);   // (v6, v7)
-            const uint32_t r = kr & 7;
-            *reinterpret_cast<uint4*>(a_tile + ng * 8192 + (kr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) = o;
-          }
-        } else if (LAYOUT == kW8N) {
-          const int wc = t & 15;
-          const uint32_t ng = wc >> 3, c = wc & 7;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int kr = (t >> 4) + 16 * i;
-            const uint2 v = reinterpret_cast<const uint2*>(raw)[kr * 16 + wc];
-            const uint32_t w2[2] = {v.x, v.y};
-            uint32_t o[4];
-#pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-              const float a = (float)(int8_t)(w2[j >> 2] >> (8 * (j & 3)));
-              const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
-              o[j >> 1] = add_mul2<XT>(X2<XT>::pack(a, b), of2[j >> 1], sc2[j >> 1], has_off);
-            }
-            const uint32_t r = kr & 7;
-            *reinterpret_cast<uint4*>(a_tile + ng * 8192 + (kr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
-                make_uint4(o[0], o[1], o[2], o[3]);
-          }
-        } else {
-          const uint32_t c = t & 7;                    // 8-wide k chunk inside the 64-deep block
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int nr = (t >> 3) + 32 * i;          // channel row inside the tile
-            const uint2 v = reinterpret_cast<const uint2*>(raw)[nr * 8 + c];
-            const uint32_t w2[2] = {v.x, v.y};
-            uint32_t o[4];
-#pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-              const float a = (float)(int8_t)(w2[j >> 2] >> (8 * (j & 3)));
-              const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
-              o[j >> 1] = add_mul2<XT>(X2<XT>::pack(a, b), of2[i], sc2[i], has_off);
-            }
-            const uint32_t r = nr & 7;
-            *reinterpret_cast<uint4*>(a_tile + (nr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
-                make_uint4(o[0], o[1], o[2], o[3]);
-          }
-        }
+        dequant_tile<LAYOUT, XT, GT>(sRaw + stage * C::kRawBytes, sA + stage * kWqABytes, lg, sc2, of2, has_off, p, g,
+                                     n_tile0);
         fence_proxy_async_smem();                      // generic-proxy stores -> visible to the MMA (async proxy)
         __syncwarp();
         if (lane == 0) mbar_arrive(&deq[stage]);
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
+      it_base += p.kblocks;
       // The stop decision is taken by all dequantising warps together (named barrier 2).
       {
         bool got = ok && mbar_wait(tfull, tphase, abort_flag, kDevTimeoutEpilogue);
@@ -363,17 +399,18 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       }
       tc_fence_after();
       tphase ^= 1;
-      // -------- epilogue: rows are channels, columns are tokens; two warps share a lane quadrant
+      // -------- epilogue: rows are channels, columns are tokens; four warps share a lane quadrant
       {
         constexpr int CH = BNX < 32 ? 16 : 32;
         constexpr int kChunks = BNX / CH;
-        const int half = dw >> 2;                      // which half of the column chunks this warp takes
+        constexpr int kShare = kWqDeqWarps / 4;        // warps sharing one TMEM lane quadrant
+        const int share = dw >> 2;                     // this warp's slot among them
         const int64_t n = n_tile0 + quad * 32 + lane;
         const bool nv = n < p.n;
         const float bias = (nv && p.bias) ? X2<XT>::to_float(static_cast<const XT*>(p.bias)[n]) : 0.0f;
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
 #pragma unroll 1
-        for (int c = half; c < kChunks; c += 2) {
+        for (int c = share; c < kChunks; c += kShare) {
           uint32_t r[CH];
           __syncwarp();
           if constexpr (CH == 32) tmem_ld_x32(taddr + c * CH, r);
