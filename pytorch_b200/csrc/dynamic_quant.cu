@@ -65,20 +65,20 @@ __device__ __forceinline__ void load_smooth8(const ST* p, float (&s)[8]) {
 }
 
 // Eight values -> eight int8 (packed), bit-exact with clamp(rint(xs / scale)).
-// Fast path: r = xs * (1/scale); adding 1.5 * 2^23 rounds r to the nearest-even integer and leaves
-// its two's-complement low byte in the low mantissa byte (|r| <= 127.0001 because scale = amax/127, so
-// no clamp is needed).  r can differ from the true quotient by a few 1e-5, so the two can only round
-// differently when r is within 2.5e-4 of a half-integer: such a vector is redone with IEEE division.
+// Fast path: fma(xs, 1/scale, 1.5 * 2^23) rounds the product to the nearest-even integer and leaves
+// its two's-complement low byte in the low mantissa byte (|xs/scale| <= 127.0001 because
+// scale = amax/127, so no clamp is needed).  The product can differ from the IEEE quotient by about
+// 2e-5, so the two can only round differently when it lies within 2.5e-4 of a half-integer: such a
+// vector is redone with IEEE division.
 __device__ __forceinline__ uint2 quantize8(const float (&f)[8], float scale, float inv) {
   constexpr float kMagic = 12582912.0f;
   uint32_t u[8];
   bool slow = false;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float r = __fmul_rn(f[j], inv);
-    const float uf = __fadd_rn(r, kMagic);
+    const float uf = __fmaf_rn(f[j], inv, kMagic);
     const float t = __fsub_rn(uf, kMagic);
-    slow |= fabsf(__fsub_rn(r, t)) > 0.49975f;
+    slow |= fabsf(__fmaf_rn(f[j], inv, -t)) > 0.49975f;
     u[j] = __float_as_uint(uf);
   }
   if (slow) {
@@ -104,81 +104,52 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 }
 
 // Vector path: k % 8 == 0 and 16-byte aligned rows.  Thread t owns vectors t, t+blockDim, ...
-// Persistent CTAs walk the rows with a stride of gridDim.x; with PREFETCH the loads of the CTA's
-// next row are issued before the arithmetic of the current one, so memory latency and the
-// quantisation arithmetic overlap inside every CTA instead of relying on neighbouring CTAs.
-template <typename T, typename ST, int ITERS, bool SMOOTH, bool PREFETCH>
+// Persistent CTAs walk the rows with a stride of gridDim.x; the packed 16-bit loads of the CTA's
+// next row are issued before the arithmetic of the current one.  The fp32 products x*smooth are
+// formed once, in the max pass, and kept in registers for the quantisation pass.  FULL means that
+// every thread's every vector is inside the row (k == 8 * ITERS * blockDim): no bounds predicates.
+template <typename T, typename ST, int ITERS, bool SMOOTH, bool FULL>
 __global__ void __launch_bounds__(512) dynamic_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth,
                                                          int8_t* __restrict__ y, float* __restrict__ scale_out,
                                                          int64_t rows, int k) {
   __shared__ float red[2][32];
   const int nvec = k >> 3;
-  uint4 cur[ITERS], nxt[ITERS];
-  auto load_row = [&](uint4 (&dst)[ITERS], int64_t row) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + row * k);
+  uint4 nxt[ITERS];
+  float f[ITERS][8];
+  auto load_row = [&](int64_t row) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * k) + threadIdx.x;
 #pragma unroll
-    for (int i = 0; i < ITERS; ++i) {
-      const int v = threadIdx.x + i * blockDim.x;
-      dst[i] = (v < nvec) ? ld_stream(xr + v) : make_uint4(0, 0, 0, 0);
-    }
+    for (int i = 0; i < ITERS; ++i)
+      nxt[i] = (FULL || threadIdx.x + i * blockDim.x < nvec) ? ld_stream(xr + i * blockDim.x) : make_uint4(0, 0, 0, 0);
   };
   int64_t row = blockIdx.x;
-  if (row < rows) load_row(cur, row);
+  if (row < rows) load_row(row);
   int par = 0;
   for (; row < rows; row += gridDim.x, par ^= 1) {
-    if (PREFETCH && row + gridDim.x < rows) load_row(nxt, row + gridDim.x);
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
       const int v = threadIdx.x + i * blockDim.x;
-      const uint32_t w[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
-      if (SMOOTH) {
-        // x*smooth is recomputed in the second pass (same fp32 product, same bits) instead of
-        // being kept: registers hold the packed 16-bit row only.
-        if (v < nvec) {
-          float sm[8];
-          load_smooth8(smooth + v * 8, sm);
+      const uint32_t w[4] = {nxt[i].x, nxt[i].y, nxt[i].z, nxt[i].w};
+      float sm[8];
+      if (SMOOTH && (FULL || v < nvec)) load_smooth8(smooth + v * 8, sm);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = unpack2<T>(w[j]);
-            amax = fmaxf(amax, fmaxf(fabsf(__fmul_rn(f.x, sm[2 * j])), fabsf(__fmul_rn(f.y, sm[2 * j + 1]))));
-          }
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = unpack2<T>(w[j]);
-          amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-        }
+      for (int j = 0; j < 4; ++j) {
+        const float2 pr = unpack2<T>(w[j]);
+        f[i][2 * j] = (SMOOTH && (FULL || v < nvec)) ? __fmul_rn(pr.x, sm[2 * j]) : pr.x;
+        f[i][2 * j + 1] = (SMOOTH && (FULL || v < nvec)) ? __fmul_rn(pr.y, sm[2 * j + 1]) : pr.y;
+        amax = fmaxf(amax, fmaxf(fabsf(f[i][2 * j]), fabsf(f[i][2 * j + 1])));
       }
     }
+    if (row + gridDim.x < rows) load_row(row + gridDim.x);   // in flight during the reduction and quantisation
     amax = block_max(amax, red[par]);
     const float scale = __fdiv_rn(amax, 127.0f);
     if (threadIdx.x == 0) scale_out[row] = scale;
     const float inv = (scale == 0.0f) ? 0.0f : __frcp_rn(scale);   // all-zero row: every product is 0
-    uint2* yr = reinterpret_cast<uint2*>(y + row * k);
+    uint2* yr = reinterpret_cast<uint2*>(y + row * k) + threadIdx.x;
 #pragma unroll
-    for (int i = 0; i < ITERS; ++i) {
-      const int v = threadIdx.x + i * blockDim.x;
-      if (v < nvec) {
-        const uint32_t w[4] = {cur[i].x, cur[i].y, cur[i].z, cur[i].w};
-        float f[8], sm[8];
-        if (SMOOTH) load_smooth8(smooth + v * 8, sm);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 pr = unpack2<T>(w[j]);
-          f[2 * j] = SMOOTH ? __fmul_rn(pr.x, sm[2 * j]) : pr.x;
-          f[2 * j + 1] = SMOOTH ? __fmul_rn(pr.y, sm[2 * j + 1]) : pr.y;
-        }
-        st_stream(yr + v, quantize8(f, scale, inv));
-      }
-    }
-    if (PREFETCH) {
-#pragma unroll
-      for (int i = 0; i < ITERS; ++i) cur[i] = nxt[i];
-    } else if (row + gridDim.x < rows) {
-      load_row(cur, row + gridDim.x);
-    }
+    for (int i = 0; i < ITERS; ++i)
+      if (FULL || threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8(f[i], scale, inv));
   }
 }
 
@@ -219,30 +190,35 @@ int launch_dq(const void* x, const void* smooth, int8_t* y, float* scale, int64_
     return check_launch("dynamic_quant (generic)");
   }
   const int nvec = (int)(k / 8);
-  // Up to eight 128-bit loads per thread and <= 256 threads per CTA where the row allows it (k <= 16384);
-  // longer rows widen the CTA to 512 threads, and beyond k = 32768 take 16 loads without prefetch.
+  // Up to four 128-bit loads per thread (32 fp32 products kept in registers) with <= 256 threads where
+  // the row allows it (k <= 8192); longer rows widen the CTA to 512 threads, then take 8 and 16 loads.
   int iters = 1;
-  while (iters < 8 && nvec > iters * 256) iters *= 2;
-  if (nvec > iters * 512) iters = 16;
+  while (iters < 4 && nvec > iters * 256) iters *= 2;
+  while (iters < 16 && nvec > iters * 512) iters *= 2;
   int threads = (int)ceil_div(nvec, iters);
   threads = (int)ceil_div(threads, 32) * 32;
+  const bool full = (int64_t)threads * iters == nvec;
   int per_sm = 1;
-#define B200Q_DQ_CASE(I, PF)                                                                                  \
-  case I: {                                                                                                    \
-    auto kern = dynamic_quant_rows<T, ST, I, SMOOTH, PF>;                                                      \
+#define B200Q_DQ_LAUNCH(I, F)                                                                                 \
+  {                                                                                                            \
+    auto kern = dynamic_quant_rows<T, ST, I, SMOOTH, F>;                                                       \
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0);                                  \
     const int64_t cap = (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);                                       \
     kern<<<(unsigned)(rows < cap ? rows : cap), threads, 0, st>>>(xp, sp, y, scale, rows, (int)k);            \
-    break;                                                                                                     \
   }
+#define B200Q_DQ_CASE(I)                                  \
+  case I:                                                 \
+    if (full) B200Q_DQ_LAUNCH(I, true) else B200Q_DQ_LAUNCH(I, false) \
+    break;
   switch (iters) {
-    B200Q_DQ_CASE(1, true)
-    B200Q_DQ_CASE(2, true)
-    B200Q_DQ_CASE(4, true)
-    B200Q_DQ_CASE(8, true)
-    B200Q_DQ_CASE(16, false)
+    B200Q_DQ_CASE(1)
+    B200Q_DQ_CASE(2)
+    B200Q_DQ_CASE(4)
+    B200Q_DQ_CASE(8)
+    B200Q_DQ_CASE(16)
   }
 #undef B200Q_DQ_CASE
+#undef B200Q_DQ_LAUNCH
   return check_launch("dynamic_quant");
 }
 

@@ -39,6 +39,10 @@ constexpr int kWqABytes = kWqTileN * kWqBK * 2;
 
 enum WqLayout { kW4N = 0, kW8N = 1, kW8K = 2 };   // int4 [k,n/8]; int8 n-contiguous; int8 k-contiguous
 
+// int4 tiles keep the nibble pairs (j, j+4) of a word together, so operand row 8q+i carries channel
+// 8q + perm(i) with perm = (0,4,1,5,2,6,3,7), i.e. perm(i) = (i >> 1) + 4 * (i & 1).
+__device__ __forceinline__ int w4_row_to_channel(int row) { return (row & ~7) + ((row & 7) >> 1) + 4 * (row & 1); }
+
 struct WqParams {
   const void* scale;     // [groups, n]
   const void* offset;    // [groups, n] or null
@@ -115,30 +119,33 @@ struct WqCfg {
   static_assert(kDynamic > 116 * 1024 || kTmemCols <= 256, "TMEM budget with two resident CTAs");
 };
 
-// Loads this thread's eight per-channel scale / offset values (fp32) for group g.
-template <typename XT>
-__device__ __forceinline__ void load_params8(const WqParams& p, int64_t g, int64_t n0, float (&sc)[8], float (&of)[8]) {
+// This thread's eight per-channel scale and offset values of group g as four 16-bit pairs each:
+// pairs (j, j+4) for int4 tiles, (2j, 2j+1) for int8 tiles.  Channels beyond n read as zero.
+template <int LAYOUT, typename XT>
+__device__ __forceinline__ void load_params8(const WqParams& p, int64_t g, int64_t n0, uint32_t (&sc2)[4],
+                                             uint32_t (&of2)[4]) {
+  uint4 s = make_uint4(0, 0, 0, 0), o = make_uint4(0, 0, 0, 0);
   if (n0 + 8 <= p.n) {
-    const uint4 s = __ldg(reinterpret_cast<const uint4*>(static_cast<const XT*>(p.scale) + g * p.n + n0));
-    const XT* sv = reinterpret_cast<const XT*>(&s);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) sc[j] = X2<XT>::to_float(sv[j]);
-    if (p.offset) {
-      const uint4 o = __ldg(reinterpret_cast<const uint4*>(static_cast<const XT*>(p.offset) + g * p.n + n0));
-      const XT* ov = reinterpret_cast<const XT*>(&o);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) of[j] = X2<XT>::to_float(ov[j]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) of[j] = 0.0f;
-    }
+    s = __ldg(reinterpret_cast<const uint4*>(static_cast<const XT*>(p.scale) + g * p.n + n0));
+    if (p.offset) o = __ldg(reinterpret_cast<const uint4*>(static_cast<const XT*>(p.offset) + g * p.n + n0));
   } else {
-#pragma unroll
+    unsigned short* sv = reinterpret_cast<unsigned short*>(&s);
+    unsigned short* ov = reinterpret_cast<unsigned short*>(&o);
     for (int j = 0; j < 8; ++j) {
-      const bool v = n0 + j < p.n;
-      sc[j] = v ? X2<XT>::to_float(static_cast<const XT*>(p.scale)[g * p.n + n0 + j]) : 0.0f;
-      of[j] = (v && p.offset) ? X2<XT>::to_float(static_cast<const XT*>(p.offset)[g * p.n + n0 + j]) : 0.0f;
+      if (n0 + j < p.n) {
+        sv[j] = static_cast<const unsigned short*>(p.scale)[g * p.n + n0 + j];
+        if (p.offset) ov[j] = static_cast<const unsigned short*>(p.offset)[g * p.n + n0 + j];
+      }
     }
+  }
+  if (LAYOUT == kW4N) {
+    sc2[0] = __byte_perm(s.x, s.z, 0x5410); sc2[1] = __byte_perm(s.x, s.z, 0x7632);
+    sc2[2] = __byte_perm(s.y, s.w, 0x5410); sc2[3] = __byte_perm(s.y, s.w, 0x7632);
+    of2[0] = __byte_perm(o.x, o.z, 0x5410); of2[1] = __byte_perm(o.x, o.z, 0x7632);
+    of2[2] = __byte_perm(o.y, o.w, 0x5410); of2[3] = __byte_perm(o.y, o.w, 0x7632);
+  } else {
+    sc2[0] = s.x; sc2[1] = s.y; sc2[2] = s.z; sc2[3] = s.w;
+    of2[0] = o.x; of2[1] = o.y; of2[2] = o.z; of2[3] = o.w;
   }
 }
 
@@ -167,13 +174,11 @@ __device__ __forceinline__ void dequant_tile(const uint8_t* __restrict__ raw, ui
 #pragma unroll
         for (int j = 0; j < 4; ++j)                    // halves of pr[j]: values j and j+4
           pr[j] = add_mul2<XT>(nibbles_to_x2<XT>(v[i] >> (4 * j)), of2[j], sc2[j], has_off);
-        uint4 o;
-        o.x = __byte_perm(pr[0], pr[1], 0x5410);       // (v0, v1)
-        o.y = __byte_perm(pr[2], pr[3], 0x5410);       // (v2, v3)
-        o.z = __byte_perm(pr[0], pr[1], 0x7632);       // (v4, v5)
-        o.w = __byte_perm(pr[2], pr[3], 0x7632);       // (v6, v7)
+        // Stored in the order (v0,v4,v1,v5,v2,v6,v3,v7): MMA row 8q+i of the tile holds channel
+        // 8q + kW4RowPerm[i]; the epilogue undoes the permutation when it computes n.
         const uint32_t r = kr & 7;
-        *reinterpret_cast<uint4*>(a_tile + ng * 8192 + (kr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) = o;
+        *reinterpret_cast<uint4*>(a_tile + ng * 8192 + (kr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
+            make_uint4(pr[0], pr[1], pr[2], pr[3]);
       }
     }
   } else if constexpr (LAYOUT == kW8N) {
@@ -366,14 +371,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const int64_t g = p.group_size > 0 ? ((int64_t)kb * kWqBK) / p.group_size : 0;
         if (LAYOUT != kW8K && g != cur_group) {
           cur_group = g;
-          float scf[8], off[8];
-          load_params8<XT>(p, g, n_tile0 + (lg & 15) * 8, scf, off);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int a = LAYOUT == kW4N ? j : 2 * j, b = LAYOUT == kW4N ? j + 4 : 2 * j + 1;
-            sc2[j] = X2<XT>::pack(scf[a], scf[b]);       // values are 16-bit already: packing is exact
-            of2[j] = X2<XT>::pack(off[a], off[b]);
-          }
+          load_params8<LAYOUT, XT>(p, g, n_tile0 + (lg & 15) * 8, sc2, of2);
         }
         // warp-uniform decision, so that the warp stays converged for __syncwarp below
         const bool got = __all_sync(0xffffffffu, mbar_wait(&full[stage], phase, abort_flag, kDevTimeoutEpilogue));
@@ -405,7 +403,8 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         constexpr int kChunks = BNX / CH;
         constexpr int kShare = kWqDeqWarps / 4;        // warps sharing one TMEM lane quadrant
         const int share = dw >> 2;                     // this warp's slot among them
-        const int64_t n = n_tile0 + quad * 32 + lane;
+        const int row = quad * 32 + lane;              // accumulator row = TMEM lane
+        const int64_t n = n_tile0 + (LAYOUT == kW4N ? w4_row_to_channel(row) : row);
         const bool nv = n < p.n;
         const float bias = (nv && p.bias) ? X2<XT>::to_float(static_cast<const XT*>(p.bias)[n]) : 0.0f;
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);

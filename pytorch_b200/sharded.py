@@ -42,14 +42,16 @@ class ColumnShardedOutput:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.m, self.n = m, n
         if self.world > 1:
-            self.staging = torch.empty((self.world, m, n // self.world), dtype=dtype, device=device)
+            # concatenation along dim 0 ([g*M, N/g]) is the output form every backend accepts
+            self.staging = torch.empty((self.world * m, n // self.world), dtype=dtype, device=device)
             self.full = torch.empty((m, n), dtype=dtype, device=device)
 
     def gather(self, shard: torch.Tensor) -> torch.Tensor:
         if self.world == 1:
             return shard
         dist.all_gather_into_tensor(self.staging, shard.contiguous(), group=self.group)
-        self.full.view(self.m, self.world, self.n // self.world).copy_(self.staging.permute(1, 0, 2))
+        per = self.n // self.world
+        self.full.view(self.m, self.world, per).copy_(self.staging.view(self.world, self.m, per).permute(1, 0, 2))
         return self.full
 
 
