@@ -91,16 +91,16 @@ __device__ __forceinline__ uint2 quantize8(const float (&f)[8], float scale, flo
   return o;
 }
 
+// Maximum of a non-negative value over the CTA.  Non-negative floats order like their bit patterns,
+// so each warp reduces with one integer redux instruction; one exchange through shared memory joins
+// the warps.
 __device__ __forceinline__ float block_max(float v, float* red) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const unsigned w = __reduce_max_sync(0xffffffffu, __float_as_uint(v));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
-  if (lane == 0) red[warp] = v;
+  if (lane == 0) red[warp] = __uint_as_float(w);
   __syncthreads();
-  float m = (lane < nwarps) ? red[lane] : 0.0f;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  return m;
+  const unsigned m = __float_as_uint((lane < nwarps) ? red[lane] : 0.0f);
+  return __uint_as_float(__reduce_max_sync(0xffffffffu, m));
 }
 
 // Vector path: k % 8 == 0 and 16-byte aligned rows.  Thread t owns vectors t, t+blockDim, ...

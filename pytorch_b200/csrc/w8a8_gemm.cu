@@ -18,6 +18,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -118,6 +120,97 @@ __device__ __forceinline__ bool epilogue_all(bool pred) {
       : "r"((uint32_t)pred), "r"(kEpiThreads)
       : "memory");
   return r != 0;
+}
+
+// Epilogue of one accumulator tile whose rows are tokens and whose columns are channels: the calling
+// thread owns row `mm` (TMEM lane taddr>>16 + lane) and walks the BN columns CH at a time; its CH results
+// are contiguous in the output row.  Column parameters come from shared memory (broadcast reads).
+// Must be called by all 32 lanes of the warp (tcgen05.ld is warp-collective).
+template <int BN, int CH>
+__device__ __forceinline__ void store_token_rows(const Epi& e, uint32_t taddr, int64_t mm, int64_t n_tile0,
+                                                 const float* col_f0, const float* col_f1, const float* col_f2,
+                                                 const int* col_i) {
+  const bool mv = mm < e.m;
+  const float pt = (mv && (e.flags & kHasPt)) ? __ldg(e.pertoken + mm) : 1.0f;
+  const bool vec = (e.flags & kOutVec) != 0;
+#pragma unroll 1
+  for (int c = 0; c < BN / CH; ++c) {
+    uint32_t r[CH];
+    __syncwarp();
+    tmem_ld_chunk<CH>(taddr + c * CH, r);
+    tmem_ld_wait();
+    const int64_t n0 = n_tile0 + c * CH;
+    if (!mv || n0 >= e.n) continue;
+    if (e.acc_ws) {
+#pragma unroll
+      for (int j = 0; j < CH; ++j)
+        if (n0 + j < e.n) atomicAdd(e.acc_ws + mm * e.n + n0 + j, (int)r[j]);
+    } else if (vec && n0 + CH <= e.n) {
+      // 128-bit stores
+      if (e.out_dtype == B200Q_I32) {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<int*>(e.out) + mm * e.n + n0);
+#pragma unroll
+        for (int q = 0; q < CH / 4; ++q)
+          dst[q] = make_uint4(r[4 * q] + col_i[c * CH + 4 * q], r[4 * q + 1] + col_i[c * CH + 4 * q + 1],
+                              r[4 * q + 2] + col_i[c * CH + 4 * q + 2], r[4 * q + 3] + col_i[c * CH + 4 * q + 3]);
+      } else if (e.out_dtype == B200Q_I8) {
+        uint32_t packed[CH / 4];
+#pragma unroll
+        for (int j = 0; j < CH; j += 4) {
+          uint32_t w = 0;
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const int cj = c * CH + j + b;
+            const float v = dequant((int)r[j + b], col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags);
+            w |= (uint32_t)(to_int8(v) & 0xFF) << (8 * b);
+          }
+          packed[j / 4] = w;
+        }
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<int8_t*>(e.out) + mm * e.n + n0);
+#pragma unroll
+        for (int q = 0; q < CH / 16; ++q)
+          dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      } else {
+        uint32_t packed[CH / 2];
+#pragma unroll
+        for (int j = 0; j < CH; j += 2) {
+          const int cj = c * CH + j;
+          const float v0 = dequant((int)r[j], col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags);
+          const float v1 =
+              dequant((int)r[j + 1], col_i[cj + 1], col_f0[cj + 1], pt, col_f2[cj + 1], col_f1[cj + 1], e.flags);
+          packed[j / 2] = to_bits16(v0, e.out_dtype) | (to_bits16(v1, e.out_dtype) << 16);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned short*>(e.out) + mm * e.n + n0);
+#pragma unroll
+        for (int q = 0; q < CH / 8; ++q)
+          dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        if (n0 + j < e.n) {
+          const int cj = c * CH + j;
+          const int acc = (int)r[j];
+          store_one(e, mm * e.n + n0 + j, acc, col_i[cj],
+                    dequant(acc, col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags));
+        }
+      }
+    }
+  }
+}
+
+// Per-channel parameters of the BN columns starting at n_tile0 -> shared memory, by the epilogue threads.
+template <int BN>
+__device__ __forceinline__ void stage_channel_params(const Epi& e, int64_t n_tile0, int et, float* col_f0, float* col_f1,
+                                                     float* col_f2, int* col_i) {
+  for (int i = et; i < BN; i += kEpiThreads) {
+    const int64_t nn = n_tile0 + i;
+    const bool v = nn < e.n;
+    col_f0[i] = v ? load_scale(e, nn) : 0.0f;
+    col_f1[i] = v ? load_offset(e, nn) : 0.0f;
+    col_f2[i] = v ? load_float_bias(e, nn) : 0.0f;
+    col_i[i] = v ? load_int_bias(e, nn) : 0;
+  }
 }
 
 template <int BN, int STAGES>
@@ -252,14 +345,7 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           col_f0[i] = ((e.flags & kHasPt) && mm < e.m) ? __ldg(e.pertoken + mm) : 1.0f;
         }
       } else {
-        for (int i = et; i < BN; i += kEpiThreads) {
-          const int64_t nn = (int64_t)tb * BN + i;
-          const bool v = nn < e.n;
-          col_f0[i] = v ? load_scale(e, nn) : 0.0f;
-          col_f1[i] = v ? load_offset(e, nn) : 0.0f;
-          col_f2[i] = v ? load_float_bias(e, nn) : 0.0f;
-          col_i[i] = v ? load_int_bias(e, nn) : 0;
-        }
+        stage_channel_params<BN>(e, (int64_t)tb * BN, et, col_f0, col_f1, col_f2, col_i);
       }
       named_barrier_sync(1, kEpiThreads);
 
@@ -296,75 +382,9 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       } else {
-        // D rows are tokens (m), D columns are channels (n): a thread owns CH consecutive n of one row.
-        const int64_t mm = (int64_t)ta * kTileA + row_in_tile;
-        const bool mv = mm < e.m;
-        const float pt = (mv && (e.flags & kHasPt)) ? __ldg(e.pertoken + mm) : 1.0f;
-        const bool vec = (e.flags & kOutVec) != 0;
-#pragma unroll 1
-        for (int c = 0; c < BN / CH; ++c) {
-          uint32_t r[CH];
-          __syncwarp();
-          tmem_ld_chunk<CH>(taddr + c * CH, r);
-          tmem_ld_wait();
-          const int64_t n0 = (int64_t)tb * BN + c * CH;
-          if (!mv || n0 >= e.n) continue;
-          if (e.acc_ws) {
-#pragma unroll
-            for (int j = 0; j < CH; ++j)
-              if (n0 + j < e.n) atomicAdd(e.acc_ws + mm * e.n + n0 + j, (int)r[j]);
-          } else if (vec && n0 + CH <= e.n) {
-            // The thread's CH results are contiguous in the output row: 128-bit stores.
-            if (e.out_dtype == B200Q_I32) {
-              uint4* dst = reinterpret_cast<uint4*>(static_cast<int*>(e.out) + mm * e.n + n0);
-#pragma unroll
-              for (int q = 0; q < CH / 4; ++q)
-                dst[q] = make_uint4(r[4 * q] + col_i[c * CH + 4 * q], r[4 * q + 1] + col_i[c * CH + 4 * q + 1],
-                                    r[4 * q + 2] + col_i[c * CH + 4 * q + 2], r[4 * q + 3] + col_i[c * CH + 4 * q + 3]);
-            } else if (e.out_dtype == B200Q_I8) {
-              uint32_t packed[CH / 4];
-#pragma unroll
-              for (int j = 0; j < CH; j += 4) {
-                uint32_t w = 0;
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                  const int cj = c * CH + j + b;
-                  const float v = dequant((int)r[j + b], col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags);
-                  w |= (uint32_t)(to_int8(v) & 0xFF) << (8 * b);
-                }
-                packed[j / 4] = w;
-              }
-              uint4* dst = reinterpret_cast<uint4*>(static_cast<int8_t*>(e.out) + mm * e.n + n0);
-#pragma unroll
-              for (int q = 0; q < CH / 16; ++q)
-                dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-            } else {
-              uint32_t packed[CH / 2];
-#pragma unroll
-              for (int j = 0; j < CH; j += 2) {
-                const int cj = c * CH + j;
-                const float v0 = dequant((int)r[j], col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags);
-                const float v1 =
-                    dequant((int)r[j + 1], col_i[cj + 1], col_f0[cj + 1], pt, col_f2[cj + 1], col_f1[cj + 1], e.flags);
-                packed[j / 2] = to_bits16(v0, e.out_dtype) | (to_bits16(v1, e.out_dtype) << 16);
-              }
-              uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned short*>(e.out) + mm * e.n + n0);
-#pragma unroll
-              for (int q = 0; q < CH / 8; ++q)
-                dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              if (n0 + j < e.n) {
-                const int cj = c * CH + j;
-                const int acc = (int)r[j];
-                store_one(e, mm * e.n + n0 + j, acc, col_i[cj],
-                          dequant(acc, col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags));
-              }
-            }
-          }
-        }
+        // D rows are tokens (m), D columns are channels (n).
+        store_token_rows<BN, CH>(e, taddr, (int64_t)ta * kTileA + row_in_tile, (int64_t)tb * BN, col_f0, col_f1, col_f2,
+                                 col_i);
       }
       tc_fence_before();
       __syncwarp();
@@ -380,6 +400,163 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Two-CTA variant for large M (cluster of two CTAs on neighbouring SMs, tcgen05 cta_group::2).
+// The pair owns a 256 x 256 output tile: each CTA loads 128 token rows of A and 128 channel rows of B
+// (its half of the B operand) per K block, so shared-memory fill and operand traffic per MMA drop by a
+// third against the one-CTA tile; the leader CTA (rank 0) issues M=256, N=256 MMAs that read both
+// halves and write 128 accumulator rows into each CTA's TMEM.  Both CTAs' TMA loads count on the
+// leader's `full` barrier; the leader's tcgen05.commit arrives on both CTAs' `empty` / `tfull`
+// barriers (one commit per CTA, no multicast); both epilogues arrive on the leader's `tempty`.
+template <int STAGES>
+struct PairLayout {
+  static constexpr int kBN = 256;
+  static constexpr int kBHalfBytes = 128 * kBK;
+  static constexpr int kStageBytes = kATileBytes + kBHalfBytes;
+  static constexpr int kTiles = STAGES * kStageBytes;
+  static constexpr int kBarOff = kTiles;
+  static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;
+  static constexpr int kColOff = kMiscOff + 16;
+  static constexpr int kTotal = kColOff + 4 * kBN * 4;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Epi e,
+                      const Sched s) {
+  using L = PairLayout<STAGES>;
+  constexpr int BN = L::kBN, CH = 32;
+  constexpr uint32_t kTmemCols = 512;
+  static_assert(L::kDynamic > 116 * 1024 && L::kDynamic <= 227 * 1024, "one CTA per SM; shared memory budget");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * kATileBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
+  float* col_f0 = reinterpret_cast<float*>(smem + L::kColOff);
+  float* col_f1 = col_f0 + BN;
+  float* col_f2 = col_f1 + BN;
+  int* col_i = reinterpret_cast<int*>(col_f2 + BN);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();                 // 0 = leader
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 2 * (kEpiThreads / 32));       // epilogue warps of both CTAs
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_holder, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                      // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = pair; u < s.units && ok; u += npairs) {
+        const int ta = u % s.tiles_a, tb = u / s.tiles_a;
+        for (int kb = 0; kb < s.kblocks; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, kDevTimeoutProducer)) { ok = false; break; }
+          if (rank == 0) mbar_arrive_expect_tx(&full[stage], 2 * L::kStageBytes);   // bytes of both CTAs
+          const uint32_t leader_full = map_to_cta(smem_u32(&full[stage]), 0);
+          tma_load_2d_pair(sA + stage * kATileBytes, &tmA, leader_full, kb * kBK, ta * 256 + (int)rank * 128);
+          tma_load_2d_pair(sB + stage * L::kBHalfBytes, &tmB, leader_full, kb * kBK, tb * 256 + (int)rank * 128);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok)
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc(2 /*s32*/, 1 /*s8*/, 1 /*s8*/, 0, 0, 256, BN);
+      int stage = 0, buf = 0;
+      uint32_t phase = 0, tphase = 0;
+      bool ok = true;
+      for (int u = pair; u < s.units && ok; u += npairs) {
+        if (!mbar_wait(&tempty[buf], tphase ^ 1, abort_flag, kDevTimeoutMma)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < s.kblocks; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, kDevTimeoutMma)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc(smem_u32(sA + stage * kATileBytes), 16, 1024, kSwizzle128B);
+          const uint64_t bdesc = make_smem_desc(smem_u32(sB + stage * L::kBHalfBytes), 16, 1024, kSwizzle128B);
+#pragma unroll
+          for (int k4 = 0; k4 < kBK / 32; ++k4)
+            umma_i8_pair(d_tmem, adesc + 2 * k4, bdesc + 2 * k4, idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+          umma_commit_pair(map_to_cta(smem_u32(&empty[stage]), 0));   // stage free in this CTA ...
+          umma_commit_pair(map_to_cta(smem_u32(&empty[stage]), 1));   // ... and in the peer
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(map_to_cta(smem_u32(&tfull[buf]), 0));
+        umma_commit_pair(map_to_cta(smem_u32(&tfull[buf]), 1));
+        if (++buf == 2) { buf = 0; tphase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
+    const int et = threadIdx.x - 64;
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    int buf = 0;
+    uint32_t tphase = 0;
+    for (int u = pair; u < s.units; u += npairs) {
+      const int ta = u % s.tiles_a, tb = u / s.tiles_a;
+      named_barrier_sync(1, kEpiThreads);
+      stage_channel_params<BN>(e, (int64_t)tb * BN, et, col_f0, col_f1, col_f2, col_i);
+      named_barrier_sync(1, kEpiThreads);
+      if (!epilogue_all(mbar_wait(&tfull[buf], tphase, abort_flag, kDevTimeoutEpilogue))) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
+      store_token_rows<BN, CH>(e, taddr, (int64_t)ta * 256 + rank * 128 + row_in_tile, (int64_t)tb * BN, col_f0, col_f1,
+                               col_f2, col_i);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[buf]), 0));
+      if (++buf == 2) { buf = 0; tphase ^= 1; }
+    }
+  }
+
+  // Teardown: neither CTA may leave while the other can still signal its barriers or read its operands.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
@@ -452,6 +629,45 @@ int launch_umma(const CUtensorMap& tmA, const CUtensorMap& tmB, const Epi& e, co
   return check_launch("quant_matmul (tcgen05)");
 }
 
+template <int STAGES>
+int launch_umma_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Epi& e, const Sched& s, cudaStream_t st) {
+  using L = PairLayout<STAGES>;
+  auto kern = w8a8_umma_pair_kernel<STAGES>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (err != cudaSuccess) return fail(B200Q_ERR_LAUNCH, "quant_matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(err));
+    configured[dev] = true;
+  }
+  // As many pairs as can be resident at once (a GPC with an odd number of free SMs leaves one unpaired).
+  static int resident_pairs[64] = {};
+  if (dev >= 0 && dev < 64 && resident_pairs[dev] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = L::kDynamic;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    resident_pairs[dev] = n < sm_count() / 2 ? n : sm_count() / 2;
+  }
+  int pairs = (dev >= 0 && dev < 64) ? resident_pairs[dev] : sm_count() / 2;
+  if (s.units < pairs) pairs = s.units;
+  kern<<<2 * pairs, kThreads, L::kDynamic, st>>>(tmA, tmB, e, s);   // cluster dims (2,1,1) are a kernel attribute
+  return check_launch("quant_matmul (tcgen05, CTA pairs)");
+}
+
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
 // Layout decision shared by the workspace query and the launch.
@@ -459,6 +675,7 @@ struct Plan {
   bool tensor_path;     // tcgen05 path usable
   bool transpose;       // contiguous [k,n] weight must be re-laid out as [n,k] first
   bool swap;            // M <= 128
+  bool pair;            // CTA-pair kernel (256 x 256 tiles)
   int bn;               // B-operand tile rows
   int splits;
   size_t ws_transpose, ws_acc;
@@ -494,6 +711,10 @@ Plan make_plan(int64_t m, int64_t k, int64_t n, int64_t sk, int64_t sn, const vo
     p.ws_acc = p.splits > 1 ? align256((size_t)m * n * 4) : 0;
   } else {
     p.bn = n <= 128 ? 128 : 256;
+    // CTA pairs pay off once there are enough 256 x 256 tiles to keep all pairs busy.
+    const char* env = getenv("B200Q_W8A8_PAIR");
+    const bool allow = env ? (env[0] != '0') : true;
+    p.pair = allow && m >= 512 && n >= 512 && ceil_div(m, 256) * ceil_div(n, 256) >= sm_count() / 2;
   }
   return p;
 }
@@ -584,9 +805,19 @@ extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream
   if (int rc = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_ptr, a->k, a_rows, a_pitch, kBK, kTileA,
                             CU_TENSOR_MAP_SWIZZLE_128B, "quant_matmul (A operand)"))
     return rc;
-  if (int rc = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_ptr, a->k, b_rows, b_pitch, kBK, p.bn,
-                            CU_TENSOR_MAP_SWIZZLE_128B, "quant_matmul (B operand)"))
+  if (int rc = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_ptr, a->k, b_rows, b_pitch, kBK,
+                            p.pair ? 128 : p.bn, CU_TENSOR_MAP_SWIZZLE_128B, "quant_matmul (B operand)"))
     return rc;
+  if (p.pair) {
+    Sched sp{};
+    sp.tiles_a = (int)ceil_div(a->m, 256);
+    sp.tiles_b = (int)ceil_div(a->n, 256);
+    sp.kblocks = (int)ceil_div(a->k, kBK);
+    sp.kb_per_split = sp.kblocks;
+    sp.splits = 1;
+    sp.units = sp.tiles_a * sp.tiles_b;
+    return launch_umma_pair<6>(tmA, tmB, e, sp, st);
+  }
 
   Sched s{};
   s.tiles_a = (int)ceil_div(a_rows, kTileA);
