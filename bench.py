@@ -51,7 +51,7 @@ def measured_peaks():
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) every 50 ms."""
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) every few ms."""
 
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
                0x80: "hw_power_brake_slowdown"}
@@ -86,7 +86,7 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop_evt.wait(0.05)
+            self._stop_evt.wait(0.004)
 
     def stop(self):
         self._stop_evt.set()
@@ -142,22 +142,35 @@ def run_b200(args):
     def ev():
         return torch.cuda.Event(enable_timing=True)
 
+    comm = torch.cuda.Stream(device=device) if world > 1 else None
+
+    def gather_async(gat, y):
+        """All-gather on the side stream so that it overlaps the next GEMM (independent data)."""
+        if world == 1:
+            return y
+        main = torch.cuda.current_stream()
+        comm.wait_stream(main)
+        y.record_stream(comm)
+        with torch.cuda.stream(comm):
+            return gat.gather(y)
+
     def step(x, x_down, record=False):
-        e = [ev() for _ in range(8)] if record else None
+        e = [ev() for _ in range(6)] if record else None
         if record: e[0].record()
         q, s = ops.npu_dynamic_quant(x, smooth_scales=d["smooth"])
         if record: e[1].record()
         y1 = ops.npu_quant_matmul(q, w_gu_t, d["s_gu"], pertoken_scale=s, output_dtype=torch.bfloat16)
         if record: e[2].record()
-        o1 = gat_gu.gather(y1)
+        o1 = gather_async(gat_gu, y1)
         if record: e[3].record()
         q2, s2 = ops.npu_dynamic_quant(x_down, smooth_scales=d["smooth_down"])
         if record: e[4].record()
         y2 = ops.npu_quant_matmul(q2, w_dn_t, d["s_dn"], pertoken_scale=s2, output_dtype=torch.bfloat16)
         if record: e[5].record()
-        o2 = gat_dn.gather(y2)
+        o2 = gather_async(gat_dn, y2)
+        if world > 1:
+            torch.cuda.current_stream().wait_stream(comm)      # the step ends when both gathers have landed
         if record:
-            e[6].record()
             dq_events.extend([(e[0], e[1]), (e[3], e[4])])
             gemm_events.extend([(e[1], e[2]), (e[4], e[5])])
         return o1, o2
@@ -208,7 +221,7 @@ def run_b200(args):
         dx.copy_(hx, non_blocking=True)
         dxd.copy_(hxd, non_blocking=True)
         o1, o2 = step(dx, dxd)
-        ho1.copy_(o1 if world > 1 else o1, non_blocking=True)
+        ho1.copy_(o1, non_blocking=True)
         ho2.copy_(o2, non_blocking=True)
 
     e2e_steps = max(3, min(args.steps, 10))
@@ -248,11 +261,16 @@ def run_b200(args):
                                    "avg_launch_ms": round(dq_ms, 4), "peak_source": peaks["source"]},
     }
     if world > 1:
-        comm_ms = ms_step - 2 * gemm_ms - 2 * dq_ms
-        out["compute_phase"] = {"ms_per_step": round(2 * gemm_ms + 2 * dq_ms, 4),
-                                "value": round(step_flops() / ((2 * gemm_ms + 2 * dq_ms) * 1e-3) / 1e12, 2), "unit": UNIT,
-                                "note": "rank-0 GEMM + dynamic-quant time only; gather and re-interleave excluded"}
-        out["gather_ms_per_step"] = round(comm_ms, 4)
+        compute_ms = 2 * gemm_ms + 2 * dq_ms
+        out["compute_phase"] = {"ms_per_step": round(compute_ms, 4),
+                                "value": round(step_flops() / (compute_ms * 1e-3) / 1e12, 2), "unit": UNIT,
+                                "note": "rank-0 GEMM + dynamic-quant kernels only (timed while the gather of the "
+                                        "other projection runs on a side stream)"}
+        out["exposed_gather_ms_per_step"] = round(ms_step - compute_ms, 4)
+        recv = (world - 1) / world * (M * 2 * FFN + M * HIDDEN) * 2
+        out["gather_link_floor_ms"] = round(recv / 770e9 * 1e3, 4)
+        out["gather_note"] = ("all_gather_into_tensor over NVLink plus one re-interleave copy per projection, on a side "
+                              "stream; link floor = bytes each GPU must receive / 770 GB/s measured peer bandwidth")
     if rank == 0 and world == 1:
         out["c2_linears_m2048"] = bench_c2(ops, device, int8_peak)
         out["cpu_baseline"] = cpu_baseline(d, sample_rows=256)

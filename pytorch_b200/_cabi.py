@@ -70,10 +70,11 @@ def lib() -> C.CDLL:
     """Loads ``lib/libb200q.so`` (raises if it has not been built)."""
     global _lib
     if _lib is None:
-        if not os.path.exists(_LIB_PATH):
-            raise ImportError(f"{_LIB_PATH} is missing: run `python -m pytorch_b200._build` "
+        path = os.environ.get("B200Q_LIB", _LIB_PATH)      # override: a differently built libb200q.so
+        if not os.path.exists(path):
+            raise ImportError(f"{path} is missing: run `python -m pytorch_b200._build` "
                               "(there is no fallback implementation)")
-        l = C.CDLL(_LIB_PATH)
+        l = C.CDLL(path)
         l.b200q_version.restype = C.c_int
         l.b200q_last_error.restype = C.c_char_p
         l.b200q_status_string.restype = C.c_char_p

@@ -5,14 +5,15 @@
 // (A operand, 128 output channels per CTA tile) and is read from HBM exactly once, still
 // packed.  Per 64-deep K block:
 //   warp 0       TMA: packed weight tile (4 KB int4 / 8 KB int8) and the activation tile
-//                [BNX tokens x 64 k] (128B swizzle) into a ring of stages
+//                [BNX tokens x 64 k] (128B swizzle) into a deep ring of load stages (up to 16, so
+//                that enough bytes are in flight from HBM)
 //   warps 2-17   in G groups, each owning every G-th K block (so G stages are in work at once):
 //                dequantise the packed tile in registers, (w + offset) * scale, and write it as
 //                a bf16/fp16 UMMA operand tile in shared memory (canonical 128B-swizzled layout;
 //                MN-major when the weight is n-contiguous, K-major when it is k-contiguous),
 //                fence.proxy.async, signal
 //   warp 1       tcgen05.mma.kind::f16 (M=128 channels, N=BNX tokens, K=16), fp32 accumulators
-//                in TMEM; tcgen05.commit frees the stage
+//                in TMEM; tcgen05.commit frees the operand slot and the load stage
 // After the last K block the dequantising warps turn into the epilogue: tcgen05.ld, bias,
 // cast, coalesced stores along n.  int4 values are expanded with the exponent-bias trick
 // (nibble placed in the mantissa of 128.0 / 1024.0, then one exact subtract); w + offset and the
@@ -99,32 +100,37 @@ __device__ __forceinline__ uint32_t nibbles_to_x2(uint32_t t) {
   return *reinterpret_cast<uint32_t*>(&w);
 }
 
+// Shared-memory plan.  Two rings: a deep one of load stages (packed weight tile + activation tile,
+// filled by TMA; its depth sets how many bytes are in flight from HBM) and a short one of operand
+// slots (dequantised weight tiles, 16 KB each, one per group of dequantising warps).
 template <int LAYOUT, int BNX>
 struct WqCfg {
   static constexpr int kRawBytes = LAYOUT == kW4N ? kWqBK * 64 : kWqBK * 128;
   static constexpr int kXBytes = BNX * 128;
-  static constexpr int kStageBytes = kWqABytes + kXBytes + kRawBytes;
-  static constexpr int kStagesWanted = (196 * 1024) / kStageBytes;
-  static constexpr int kStages = kStagesWanted > 8 ? 8 : kStagesWanted;
+  static constexpr int kLoadBytes = kRawBytes + kXBytes;
+  static constexpr int kASlots = 4;
+  static constexpr int kLoadWanted = (200 * 1024 - kASlots * kWqABytes) / kLoadBytes;
+  static constexpr int kLoadStages = kLoadWanted > 16 ? 16 : kLoadWanted;
   static constexpr int kAOff = 0;
-  static constexpr int kXOff = kStages * kWqABytes;
-  static constexpr int kRawOff = kXOff + kStages * kXBytes;
-  static constexpr int kBarOff = kRawOff + kStages * kRawBytes;   // full, deq, empty per stage; tfull; tempty
-  static constexpr int kMiscOff = kBarOff + (3 * kStages + 2) * 8;
+  static constexpr int kXOff = kASlots * kWqABytes;
+  static constexpr int kRawOff = kXOff + kLoadStages * kXBytes;
+  static constexpr int kBarOff = kRawOff + kLoadStages * kRawBytes;   // full[L], lfree[L], aready[A], afree[A], tfull, tempty
+  static constexpr int kMiscOff = kBarOff + (2 * kLoadStages + 2 * kASlots + 2) * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kDynamic = kTotal + 1024;
   static constexpr uint32_t kTmemCols = BNX < 32 ? 32 : BNX;
-  static_assert(kStages >= 2, "pipeline needs at least two stages");
+  static_assert(kLoadStages >= 2, "pipeline needs at least two load stages");
   static_assert(kDynamic <= 227 * 1024, "shared memory budget");
   static_assert(kDynamic > 116 * 1024 || kTmemCols <= 256, "TMEM budget with two resident CTAs");
 };
 
-// This thread's eight per-channel scale and offset values of group g as four 16-bit pairs each:
-// pairs (j, j+4) for int4 tiles, (2j, 2j+1) for int8 tiles.  Channels beyond n read as zero.
-template <int LAYOUT, typename XT>
-__device__ __forceinline__ void load_params8(const WqParams& p, int64_t g, int64_t n0, uint32_t (&sc2)[4],
-                                             uint32_t (&of2)[4]) {
-  uint4 s = make_uint4(0, 0, 0, 0), o = make_uint4(0, 0, 0, 0);
+// Fetches this thread's eight per-channel scale and offset values of group g (raw 16-bit values;
+// channels beyond n read as zero).  Kept separate from pair_params8 so that the loads for the next
+// K block can be in flight while the current one is dequantised.
+template <typename XT>
+__device__ __forceinline__ void fetch_params8(const WqParams& p, int64_t g, int64_t n0, uint4& s, uint4& o) {
+  s = make_uint4(0, 0, 0, 0);
+  o = make_uint4(0, 0, 0, 0);
   if (n0 + 8 <= p.n) {
     s = __ldg(reinterpret_cast<const uint4*>(static_cast<const XT*>(p.scale) + g * p.n + n0));
     if (p.offset) o = __ldg(reinterpret_cast<const uint4*>(static_cast<const XT*>(p.offset) + g * p.n + n0));
@@ -138,6 +144,10 @@ __device__ __forceinline__ void load_params8(const WqParams& p, int64_t g, int64
       }
     }
   }
+}
+// Arranges the fetched values as four 16-bit pairs each: (j, j+4) for int4 tiles, (2j, 2j+1) for int8.
+template <int LAYOUT>
+__device__ __forceinline__ void pair_params8(const uint4& s, const uint4& o, uint32_t (&sc2)[4], uint32_t (&of2)[4]) {
   if (LAYOUT == kW4N) {
     sc2[0] = __byte_perm(s.x, s.z, 0x5410); sc2[1] = __byte_perm(s.x, s.z, 0x7632);
     sc2[2] = __byte_perm(s.y, s.w, 0x5410); sc2[3] = __byte_perm(s.y, s.w, 0x7632);
@@ -247,7 +257,7 @@ template <int LAYOUT, typename XT, int BNX>
 __global__ void __launch_bounds__(kWqThreads, 1)
 wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const WqParams p) {
   using C = WqCfg<LAYOUT, BNX>;
-  constexpr int STAGES = C::kStages;
+  constexpr int LS = C::kLoadStages, AS = C::kASlots;
   constexpr bool A_MN = LAYOUT != kW8K;
 
   extern __shared__ uint8_t smem_raw[];
@@ -256,19 +266,23 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   uint8_t* sX = smem + C::kXOff;
   uint8_t* sRaw = smem + C::kRawOff;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kBarOff);
-  uint64_t* deq = full + STAGES;
-  uint64_t* empty = deq + STAGES;
-  uint64_t* tfull = empty + STAGES;
+  uint64_t* lfree = full + LS;
+  uint64_t* aready = lfree + LS;
+  uint64_t* afree = aready + AS;
+  uint64_t* tfull = afree + AS;
   uint64_t* tempty = tfull + 1;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + C::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::kMiscOff + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < STAGES; ++i) {
+    for (int i = 0; i < LS; ++i) {
       mbar_init(&full[i], 1);
-      mbar_init(&deq[i], kWqDeqWarps / (STAGES >= 8 ? 8 : STAGES >= 4 ? 4 : 2));
-      mbar_init(&empty[i], 1);
+      mbar_init(&lfree[i], 1);
+    }
+    for (int i = 0; i < AS; ++i) {
+      mbar_init(&aready[i], kWqDeqWarps / (LS > AS ? AS : 2));
+      mbar_init(&afree[i], 1);
     }
     mbar_init(tfull, 1);
     mbar_init(tempty, kWqDeqWarps);
@@ -295,7 +309,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
         const int tn = u % p.tiles_n, mc = u / p.tiles_n;
         for (int kb = 0; kb < p.kblocks; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, kDevTimeoutProducer)) { ok = false; break; }
+          if (!mbar_wait(&lfree[stage], phase ^ 1, abort_flag, kDevTimeoutProducer)) { ok = false; break; }
           mbar_arrive_expect_tx(&full[stage], C::kRawBytes + C::kXBytes);
           if (LAYOUT == kW4N)        // bytes of packed nibbles: 64 bytes = 128 channels per row of k
             tma_load_2d(sRaw + stage * C::kRawBytes, &tmW, &full[stage], tn * 64, kb * kWqBK);
@@ -304,7 +318,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           else                       // k-contiguous: rows are channels
             tma_load_2d(sRaw + stage * C::kRawBytes, &tmW, &full[stage], kb * kWqBK, tn * kWqTileN);
           tma_load_2d(sX + stage * C::kXBytes, &tmX, &full[stage], kb * kWqBK, mc * BNX);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == LS) { stage = 0; phase ^= 1; }
         }
       }
       if (!ok)
@@ -315,17 +329,17 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (lane == 0) {
       constexpr uint32_t fmt = sizeof(XT) == 2 && std::is_same<XT, __nv_bfloat16>::value ? 1u : 0u;
       constexpr uint32_t idesc = make_idesc(1 /*f32*/, fmt, fmt, A_MN ? 1 : 0, 0, kWqTileN, BNX);
-      int stage = 0;
-      uint32_t phase = 0, tphase = 0;
+      int stage = 0, slot = 0;
+      uint32_t phase = 0, aphase = 0, tphase = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
         if (!mbar_wait(tempty, tphase ^ 1, abort_flag, kDevTimeoutMma)) { ok = false; break; }
         tc_fence_after();
         for (int kb = 0; kb < p.kblocks; ++kb) {
-          if (!mbar_wait(&deq[stage], phase, abort_flag, kDevTimeoutMma) ||
+          if (!mbar_wait(&aready[slot], aphase, abort_flag, kDevTimeoutMma) ||
               !mbar_wait(&full[stage], phase, abort_flag, kDevTimeoutMma)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sA + stage * kWqABytes), b_addr = smem_u32(sX + stage * C::kXBytes);
+          const uint32_t a_addr = smem_u32(sA + slot * kWqABytes), b_addr = smem_u32(sX + stage * C::kXBytes);
 #pragma unroll
           for (int k16 = 0; k16 < kWqBK / 16; ++k16) {
             // MN-major A: 16 k = two 8-row groups of 1024 B; 64-channel groups 8192 B apart.
@@ -333,10 +347,14 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const uint64_t adesc = A_MN ? make_smem_desc(a_addr + k16 * 2048, 8192, 1024, kSwizzle128B)
                                         : make_smem_desc(a_addr + k16 * 32, 16, 1024, kSwizzle128B);
             const uint64_t bdesc = make_smem_desc(b_addr + k16 * 32, 16, 1024, kSwizzle128B);
+#if !(defined(B200Q_DIAG) && (B200Q_DIAG & 2))
             umma_f16(tmem_base, adesc, bdesc, idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
+#endif
           }
-          umma_commit(&empty[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          umma_commit(&afree[slot]);                     // operand slot may be overwritten ...
+          umma_commit(&lfree[stage]);                    // ... and the load stage refilled
+          if (++stage == LS) { stage = 0; phase ^= 1; }
+          if (++slot == AS) { slot = 0; aphase ^= 1; }
         }
         if (!ok) break;
         umma_commit(tfull);
@@ -345,9 +363,11 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     }
   } else {
     // ------------------------------------------- dequantise, then epilogue
-    // The sixteen warps form G groups; group g owns every G-th K block, so G stages are being
-    // dequantised at the same time and no warp waits for another inside a stage.
-    constexpr int G = STAGES >= 8 ? 8 : STAGES >= 4 ? 4 : 2;
+    // The sixteen warps form G groups; group g owns every G-th K block, so G tiles are being
+    // dequantised at the same time and no warp waits for another inside a tile.  G stays below the
+    // number of load stages: a group must never wait for a phase of a `full` barrier while that
+    // barrier is still a whole phase behind (the parity test could not tell the two apart).
+    constexpr int G = LS > AS ? AS : 2;
     constexpr int WG = kWqDeqWarps / G;                // warps per group
     constexpr int GT = WG * 32;                        // threads per group
     const int dw = warp - 2;                           // 0..15
@@ -363,24 +383,42 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       const int64_t n_tile0 = (int64_t)tn * kWqTileN;
       int64_t cur_group = -1;
       uint32_t sc2[4], of2[4];   // this thread's 8 channels as 16-bit pairs: kW4N (j, j+4), kW8N (2j, 2j+1)
-      for (int kb = 0; kb < p.kblocks; ++kb) {
+      uint4 ns, no;              // parameters fetched ahead for the next K block of this group
+      const int64_t n_oct0 = n_tile0 + (lg & 15) * 8;
+      auto quant_group = [&](int kb) -> int64_t { return p.group_size > 0 ? ((int64_t)kb * kWqBK) / p.group_size : 0; };
+      int kb = (group - it_base % G + G) % G;          // first K block of this tile owned by the group
+      int64_t g_next = quant_group(kb);
+      if (LAYOUT != kW8K && kb < p.kblocks) fetch_params8<XT>(p, g_next, n_oct0, ns, no);
+      for (; kb < p.kblocks; kb += G) {
         const int it = it_base + kb;
-        if ((it % G) != group) continue;
-        const int stage = it % STAGES;
-        const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
-        const int64_t g = p.group_size > 0 ? ((int64_t)kb * kWqBK) / p.group_size : 0;
-        if (LAYOUT != kW8K && g != cur_group) {
-          cur_group = g;
-          load_params8<LAYOUT, XT>(p, g, n_tile0 + (lg & 15) * 8, sc2, of2);
+        const int stage = it % LS;
+        const uint32_t phase = (uint32_t)(it / LS) & 1u;
+        const int slot = it % AS;
+        const uint32_t aphase = (uint32_t)(it / AS) & 1u;
+        const int64_t g = g_next;
+        if (LAYOUT != kW8K) {
+          if (g != cur_group) {
+            cur_group = g;
+            pair_params8<LAYOUT>(ns, no, sc2, of2);
+          }
+          if (kb + G < p.kblocks) {                    // loads for the group's next K block fly during this one
+            g_next = quant_group(kb + G);
+            if (g_next != g) fetch_params8<XT>(p, g_next, n_oct0, ns, no);
+          }
+        } else if (kb + G < p.kblocks) {
+          g_next = quant_group(kb + G);
         }
         // warp-uniform decision, so that the warp stays converged for __syncwarp below
-        const bool got = __all_sync(0xffffffffu, mbar_wait(&full[stage], phase, abort_flag, kDevTimeoutEpilogue));
+        const bool got = __all_sync(0xffffffffu, mbar_wait(&full[stage], phase, abort_flag, kDevTimeoutEpilogue) &&
+                                                     mbar_wait(&afree[slot], aphase ^ 1, abort_flag, kDevTimeoutEpilogue));
         if (!got) { ok = false; break; }
-        dequant_tile<LAYOUT, XT, GT>(sRaw + stage * C::kRawBytes, sA + stage * kWqABytes, lg, sc2, of2, has_off, p, g,
+#if !(defined(B200Q_DIAG) && (B200Q_DIAG & 1))
+        dequant_tile<LAYOUT, XT, GT>(sRaw + stage * C::kRawBytes, sA + slot * kWqABytes, lg, sc2, of2, has_off, p, g,
                                      n_tile0);
+#endif
         fence_proxy_async_smem();                      // generic-proxy stores -> visible to the MMA (async proxy)
         __syncwarp();
-        if (lane == 0) mbar_arrive(&deq[stage]);
+        if (lane == 0) mbar_arrive(&aready[slot]);
       }
       it_base += p.kblocks;
       // The stop decision is taken by all dequantising warps together (named barrier 2).
