@@ -250,7 +250,7 @@ def run_b200(args):
         "clocks": clocks,
         "e2e": e2e,
         "gpu_launches": 4 * args.steps,
-        "roofline": {"bound": "tensor", "kernel": "w8a8_umma_kernel", "achieved": round(gemm_flops_per_launch / (gemm_ms * 1e-3) / 1e12, 1),
+        "roofline": {"bound": "tensor", "kernel": "w8a8_umma_pair_kernel", "achieved": round(gemm_flops_per_launch / (gemm_ms * 1e-3) / 1e12, 1),
                      "peak": round(int8_peak, 1), "unit": "TOP/s", "frac": round(gemm_flops_per_launch / (gemm_ms * 1e-3) / 1e12 / int8_peak, 4),
                      "traffic": None,
                      "peak_source": f"2 x bf16_tflops_sustained ({peaks['source']}); int8 runs at twice the bf16 rate on B200",
