@@ -73,15 +73,15 @@ __device__ __forceinline__ void load_smooth8(const ST* p, float (&s)[8]) {
 __device__ __forceinline__ uint2 quantize8(const float (&f)[8], float scale, float inv) {
   constexpr float kMagic = 12582912.0f;
   uint32_t u[8];
-  bool slow = false;
+  float dist = 0.0f;                                   // largest distance of a product from its rounded value
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float uf = __fmaf_rn(f[j], inv, kMagic);
     const float t = __fsub_rn(uf, kMagic);
-    slow |= fabsf(__fmaf_rn(f[j], inv, -t)) > 0.49975f;
+    dist = fmaxf(dist, fabsf(__fmaf_rn(f[j], inv, -t)));
     u[j] = __float_as_uint(uf);
   }
-  if (slow) {
+  if (dist > 0.49975f) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) u[j] = (uint32_t)__float2int_rn(__fdiv_rn(f[j], scale));
   }
@@ -109,7 +109,7 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // formed once, in the max pass, and kept in registers for the quantisation pass.  FULL means that
 // every thread's every vector is inside the row (k == 8 * ITERS * blockDim): no bounds predicates.
 template <typename T, typename ST, int ITERS, bool SMOOTH, bool FULL>
-__global__ void __launch_bounds__(512) dynamic_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth,
+__global__ void __launch_bounds__(ITERS == 4 ? 1024 : 512) dynamic_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth,
                                                          int8_t* __restrict__ y, float* __restrict__ scale_out,
                                                          int64_t rows, int k) {
   __shared__ float red[2][32];
@@ -191,10 +191,12 @@ int launch_dq(const void* x, const void* smooth, int8_t* y, float* scale, int64_
   }
   const int nvec = (int)(k / 8);
   // Up to four 128-bit loads per thread (32 fp32 products kept in registers) with <= 256 threads where
-  // the row allows it (k <= 8192); longer rows widen the CTA to 512 threads, then take 8 and 16 loads.
+  // the row allows it (k <= 8192); longer rows widen the CTA up to 1024 threads (k <= 32768), then take
+  // 8 and 16 loads per thread with 512 threads.
   int iters = 1;
   while (iters < 4 && nvec > iters * 256) iters *= 2;
-  while (iters < 16 && nvec > iters * 512) iters *= 2;
+  if (nvec > 4 * 1024)                                   // k > 32768: more loads per thread
+    while (iters < 16 && nvec > iters * 512) iters *= 2;
   int threads = (int)ceil_div(nvec, iters);
   threads = (int)ceil_div(threads, 32) * 32;
   const bool full = (int64_t)threads * iters == nvec;
