@@ -1,26 +1,32 @@
 // npu_weight_quant_batchmatmul: weight-only quantised matmul (int4-packed W4A16, int8 W8A16)
 // fused into one tcgen05 kernel.
 //
-// The quantised weight is the dominant traffic, so it takes the 128-row axis of the MMA
-// (A operand, 128 output channels per CTA tile) and is read from HBM exactly once, still
-// packed.  Per 64-deep K block:
-//   warp 0       TMA: packed weight tile (4 KB int4 / 8 KB int8) and the activation tile
-//                [BNX tokens x 64 k] (128B swizzle) into a deep ring of load stages (up to 16, so
-//                that enough bytes are in flight from HBM)
-//   warps 2-17   in G groups, each owning every G-th K block (so G stages are in work at once):
-//                dequantise the packed tile in registers, (w + offset) * scale, and write it as
-//                a bf16/fp16 UMMA operand tile in shared memory (canonical 128B-swizzled layout;
-//                MN-major when the weight is n-contiguous, K-major when it is k-contiguous),
-//                fence.proxy.async, signal
-//   warp 1       tcgen05.mma.kind::f16 (M=128 channels, N=BNX tokens, K=16), fp32 accumulators
-//                in TMEM; tcgen05.commit frees the operand slot and the load stage
-// After the last K block the dequantising warps turn into the epilogue: tcgen05.ld, bias,
-// cast, coalesced stores along n.  int4 values are expanded with the exponent-bias trick
-// (nibble placed in the mantissa of 128.0 / 1024.0, then one exact subtract); w + offset and the
-// product with scale are packed 16-bit operations, rounded exactly as the reference's golden does.
+// The packed weight is read from HBM exactly once.  Tokens sit on the M axis of the MMA (M = 64
+// for up to 64 tokens, else 128 per chunk), 256 output channels on the N axis, so one
+// tcgen05.mma.kind::f16 (K = 16) covers 256 channels and the fixed issue cost of an MMA is spread
+// over 4096 weights.  Per 64-deep K block of a 256-channel tile:
+//   warp 0       TMA: packed weight tile (8 KB int4 / 16 KB int8) and the activation tile
+//                [M tokens x 64 k] (128B swizzle) into a ring of load stages
+//   warps 2-17   two groups of eight warps, each owning every second K block: dequantise the packed
+//                tile in registers, (w + offset) * scale, and write it as the bf16/fp16 B operand in
+//                shared memory (canonical 128B-swizzled UMMA layout; MN-major when the weight is
+//                n-contiguous, K-major when it is k-contiguous), fence.proxy.async, signal
+//   warp 1       tcgen05.mma (fp32 accumulators in TMEM); one tcgen05.commit per K block frees
+//                the load stage and the operand slot
+// Work is split stream-K style when there are few tiles: the (tile, K block) space is cut into
+// equal contiguous ranges, one per CTA, so all SMs stream weights.  A CTA that covers a tile's whole
+// K range writes the output itself; otherwise it stores an fp32 partial tile into caller workspace
+// (slot = its position among the CTAs sharing the tile) and wq_finalize_kernel adds the partials
+// in a fixed order: the result does not depend on timing.
+// The dequantising warps also run the epilogue (tcgen05.ld, bias, cast, 64-byte row segments).
+// int4 values are expanded with the exponent-bias trick (nibble placed in the mantissa of
+// 128.0 / 1024.0, then one exact subtract); w + offset and the product with scale are packed 16-bit
+// operations, rounded exactly as the reference's golden does.
 // All mbarrier waits are bounded (see ptx.cuh).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+
+#include <stdlib.h>
 
 #include <type_traits>
 
@@ -31,28 +37,87 @@
 namespace b200q {
 namespace {
 
+// Optional cycle accounting of the pipeline roles of CTA 0 (diagnostic builds only).
+#ifdef B200Q_DIAG_TIMING
+__device__ unsigned long long g_wq_diag[16];
+#define WQ_DIAG_BEGIN() long long diag_t0 = clock64()
+#define WQ_DIAG_ADD(var) do { long long diag_t1 = clock64(); (var) += diag_t1 - diag_t0; diag_t0 = diag_t1; } while (0)
+#define WQ_DIAG_STORE(idx, var) do { if (blockIdx.x == 0) g_wq_diag[idx] = (unsigned long long)(var); } while (0)
+#else
+#define WQ_DIAG_BEGIN() do {} while (0)
+#define WQ_DIAG_ADD(var) do {} while (0)
+#define WQ_DIAG_STORE(idx, var) do {} while (0)
+#endif
+
 constexpr int kWqBK = 64;                   // K elements per stage (one 128-byte swizzle row of bf16)
-constexpr int kWqTileN = 128;               // output channels per tile = UMMA M
+constexpr int kWqTileN = 256;               // output channels per tile = UMMA N
 constexpr int kWqDeqWarps = 16;
+constexpr int kWqGroups = 2;                // groups of dequantising warps
+constexpr int kWqGroupThreads = kWqDeqWarps / kWqGroups * 32;
 constexpr int kWqDeqThreads = kWqDeqWarps * 32;
 constexpr int kWqThreads = 64 + kWqDeqThreads;
-constexpr int kWqABytes = kWqTileN * kWqBK * 2;
+constexpr int kWqBBytes = kWqTileN * kWqBK * 2;   // one dequantised operand tile
 
 enum WqLayout { kW4N = 0, kW8N = 1, kW8K = 2 };   // int4 [k,n/8]; int8 n-contiguous; int8 k-contiguous
-
-// int4 tiles keep the nibble pairs (j, j+4) of a word together, so operand row 8q+i carries channel
-// 8q + perm(i) with perm = (0,4,1,5,2,6,3,7), i.e. perm(i) = (i >> 1) + 4 * (i & 1).
-__device__ __forceinline__ int w4_row_to_channel(int row) { return (row & ~7) + ((row & 7) >> 1) + 4 * (row & 1); }
 
 struct WqParams {
   const void* scale;     // [groups, n]
   const void* offset;    // [groups, n] or null
   const void* bias;      // [n] or null
   void* out;             // [m, n]
+  float* parts;          // stream-K partial tiles [max_parts][m][n] fp32, or null
   int64_t m, n, k;
   int64_t group_size;    // 0: per channel
+  int64_t total_items;   // units * kblocks
   int tiles_n, m_chunks, kblocks, units;
+  int stream_k;          // 1: contiguous item ranges per CTA; 0: whole units round-robin
+  int ctas;              // grid size the partition was planned for
 };
+
+// Which K blocks of which unit a CTA works on, in order.  Every role of the CTA walks the same
+// sequence.  stream-K: CTA c owns items [c*T/G, (c+1)*T/G) of the linearised (unit, K block) space.
+struct WqWalk {
+  int64_t i, end;
+  int u, units, step, kblocks;
+  bool stream_k;
+  __device__ WqWalk(const WqParams& p, int cta, int grid) {
+    stream_k = p.stream_k != 0;
+    kblocks = p.kblocks;
+    units = p.units;
+    if (stream_k) {
+      i = (int64_t)cta * p.total_items / grid;
+      end = (int64_t)(cta + 1) * p.total_items / grid;
+    } else {
+      i = 0; end = 0;
+    }
+    u = cta;
+    step = grid;
+  }
+  // Next segment: unit, first and one-past-last K block.  Returns false when the CTA is done.
+  __device__ bool next(int& unit, int& kb0, int& kb1) {
+    if (stream_k) {
+      if (i >= end) return false;
+      unit = (int)(i / kblocks);
+      kb0 = (int)(i - (int64_t)unit * kblocks);
+      const int64_t left = end - i;
+      kb1 = (left < kblocks - kb0) ? kb0 + (int)left : kblocks;
+      i += kb1 - kb0;
+      return true;
+    }
+    if (u >= units) return false;
+    unit = u; kb0 = 0; kb1 = kblocks;
+    u += step;
+    return true;
+  }
+};
+
+// stream-K: the CTA whose range contains `item`.
+__host__ __device__ inline int wq_cta_of_item(int64_t item, int64_t total, int grid) {
+  int c = (int)((item * grid) / total);
+  while (c + 1 < grid && (int64_t)(c + 1) * total / grid <= item) ++c;
+  while (c > 0 && (int64_t)c * total / grid > item) --c;
+  return c;
+}
 
 template <typename XT>
 struct X2;
@@ -100,30 +165,6 @@ __device__ __forceinline__ uint32_t nibbles_to_x2(uint32_t t) {
   return *reinterpret_cast<uint32_t*>(&w);
 }
 
-// Shared-memory plan.  Two rings: a deep one of load stages (packed weight tile + activation tile,
-// filled by TMA; its depth sets how many bytes are in flight from HBM) and a short one of operand
-// slots (dequantised weight tiles, 16 KB each, one per group of dequantising warps).
-template <int LAYOUT, int BNX>
-struct WqCfg {
-  static constexpr int kRawBytes = LAYOUT == kW4N ? kWqBK * 64 : kWqBK * 128;
-  static constexpr int kXBytes = BNX * 128;
-  static constexpr int kLoadBytes = kRawBytes + kXBytes;
-  static constexpr int kASlots = 4;
-  static constexpr int kLoadWanted = (200 * 1024 - kASlots * kWqABytes) / kLoadBytes;
-  static constexpr int kLoadStages = kLoadWanted > 16 ? 16 : kLoadWanted;
-  static constexpr int kAOff = 0;
-  static constexpr int kXOff = kASlots * kWqABytes;
-  static constexpr int kRawOff = kXOff + kLoadStages * kXBytes;
-  static constexpr int kBarOff = kRawOff + kLoadStages * kRawBytes;   // full[L], lfree[L], aready[A], afree[A], tfull, tempty
-  static constexpr int kMiscOff = kBarOff + (2 * kLoadStages + 2 * kASlots + 2) * 8;
-  static constexpr int kTotal = kMiscOff + 16;
-  static constexpr int kDynamic = kTotal + 1024;
-  static constexpr uint32_t kTmemCols = BNX < 32 ? 32 : BNX;
-  static_assert(kLoadStages >= 2, "pipeline needs at least two load stages");
-  static_assert(kDynamic <= 227 * 1024, "shared memory budget");
-  static_assert(kDynamic > 116 * 1024 || kTmemCols <= 256, "TMEM budget with two resident CTAs");
-};
-
 // Fetches this thread's eight per-channel scale and offset values of group g (raw 16-bit values;
 // channels beyond n read as zero).  Kept separate from pair_params8 so that the loads for the next
 // K block can be in flight while the current one is dequantised.
@@ -159,65 +200,82 @@ __device__ __forceinline__ void pair_params8(const uint4& s, const uint4& o, uin
   }
 }
 
-// Dequantises one packed [64 k x 128 n] tile into the UMMA operand tile, using the GT threads of a
-// warp group (thread index lg).  Packed words are fetched in batches of eight before any arithmetic
-// so that the shared-memory latency and the dependent 16-bit operations of different items overlap.
+// int4 tiles keep the nibble pairs (j, j+4) of a word together, so operand row (= accumulator
+// column) 8q+i carries channel 8q + perm(i), perm = (0,4,1,5,2,6,3,7); column of channel 8q+o is
+// 8q + inv(o) with inv(o) = ((o & 3) << 1) | (o >> 2).
+__host__ __device__ constexpr int w4_channel_to_column(int o) { return (o & ~7) + (((o & 3) << 1) | ((o & 7) >> 2)); }
+
+// Shared-memory plan: AS operand slots (32 KB each) and LS load stages (packed weight tile +
+// activation tile).  LS > AS so that a group never waits on a barrier a whole phase behind.
+template <int LAYOUT, int MM, int NCH>
+struct WqCfg {
+  static constexpr int kRawBytes = LAYOUT == kW4N ? kWqBK * 128 : kWqBK * 256;
+  static constexpr int kXBytes = NCH * MM * 128;            // NCH token chunks of MM rows share one weight tile
+  static constexpr int kLoadBytes = kRawBytes + kXBytes;
+  static constexpr int kBudget = 212 * 1024;
+  static constexpr int kLS3 = (kBudget - 3 * kWqBBytes) / kLoadBytes;
+  static constexpr int kASlots = kLS3 > 3 ? 3 : 2;
+  static constexpr int kLoadWanted = (kBudget - kASlots * kWqBBytes) / kLoadBytes;
+  static constexpr int kLoadStages = kLoadWanted > 12 ? 12 : kLoadWanted;
+  static constexpr int kBOff = 0;
+  static constexpr int kXOff = kASlots * kWqBBytes;
+  static constexpr int kRawOff = kXOff + kLoadStages * kXBytes;
+  static constexpr int kBarOff = kRawOff + kLoadStages * kRawBytes;   // full[L], done[L], aready[A], tfull, tempty
+  static constexpr int kMiscOff = kBarOff + (2 * kLoadStages + kASlots + 2) * 8;
+  static constexpr int kTotal = kMiscOff + 16;
+  static constexpr int kDynamic = kTotal + 1024;
+  static constexpr uint32_t kTmemCols = NCH * kWqTileN;
+  static_assert(kLoadStages > kASlots && kLoadStages > kWqGroups, "ring depths");
+  static_assert(kDynamic <= 227 * 1024 && kDynamic > 116 * 1024, "shared memory budget; one CTA per SM");
+};
+
+// Dequantises one packed [64 k x 256 n] tile into the UMMA B-operand tile with the GT threads of a
+// warp group (thread index lg).  Packed words are fetched in batches before any arithmetic so that
+// shared-memory latency and the dependent 16-bit operations of different items overlap.
 template <int LAYOUT, typename XT, int GT>
-__device__ __forceinline__ void dequant_tile(const uint8_t* __restrict__ raw, uint8_t* __restrict__ a_tile, int lg,
+__device__ __forceinline__ void dequant_tile(const uint8_t* __restrict__ raw, uint8_t* __restrict__ b_tile, int lg,
                                              const uint32_t (&sc2)[4], const uint32_t (&of2)[4], bool has_off,
                                              const WqParams& p, int64_t g, int64_t n_tile0) {
-  constexpr int ITEMS = (kWqBK * 16) / GT;             // 8-value items per thread (1024 per tile)
+  constexpr int ITEMS = (kWqBK * (kWqTileN / 8)) / GT;      // 8-value items per thread (2048 per tile)
   constexpr int BATCH = ITEMS < 8 ? ITEMS : 8;
-  if constexpr (LAYOUT == kW4N) {
-    const int wc = lg & 15;                            // 8-channel group inside the tile
-    const uint32_t ng = wc >> 3, c = wc & 7;
-    const uint32_t* raw32 = reinterpret_cast<const uint32_t*>(raw);
-#pragma unroll
-    for (int b0 = 0; b0 < ITEMS; b0 += BATCH) {
-      uint32_t v[BATCH];
-#pragma unroll
-      for (int i = 0; i < BATCH; ++i) v[i] = raw32[((lg >> 4) + (GT / 16) * (b0 + i)) * 16 + wc];
-#pragma unroll
-      for (int i = 0; i < BATCH; ++i) {
-        const int kr = (lg >> 4) + (GT / 16) * (b0 + i);
-        uint32_t pr[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)                    // halves of pr[j]: values j and j+4
-          pr[j] = add_mul2<XT>(nibbles_to_x2<XT>(v[i] >> (4 * j)), of2[j], sc2[j], has_off);
-        // Stored in the order (v0,v4,v1,v5,v2,v6,v3,v7): MMA row 8q+i of the tile holds channel
-        // 8q + kW4RowPerm[i]; the epilogue undoes the permutation when it computes n.
-        const uint32_t r = kr & 7;
-        *reinterpret_cast<uint4*>(a_tile + ng * 8192 + (kr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
-            make_uint4(pr[0], pr[1], pr[2], pr[3]);
-      }
-    }
-  } else if constexpr (LAYOUT == kW8N) {
-    const int wc = lg & 15;
-    const uint32_t ng = wc >> 3, c = wc & 7;
-    const uint2* raw64 = reinterpret_cast<const uint2*>(raw);
+  if constexpr (LAYOUT != kW8K) {
+    const int wc = lg & 31;                                  // 8-channel group inside the tile
+    const uint32_t ng = wc >> 3, c = wc & 7;                 // 64-channel block, 16-byte chunk in its 128-byte row
 #pragma unroll
     for (int b0 = 0; b0 < ITEMS; b0 += BATCH) {
       uint2 v[BATCH];
 #pragma unroll
-      for (int i = 0; i < BATCH; ++i) v[i] = raw64[((lg >> 4) + (GT / 16) * (b0 + i)) * 16 + wc];
+      for (int i = 0; i < BATCH; ++i) {
+        const int kr = (lg >> 5) + (GT / 32) * (b0 + i);
+        if constexpr (LAYOUT == kW4N) v[i] = make_uint2(reinterpret_cast<const uint32_t*>(raw)[kr * 32 + wc], 0u);
+        else v[i] = reinterpret_cast<const uint2*>(raw)[kr * 32 + wc];
+      }
 #pragma unroll
       for (int i = 0; i < BATCH; ++i) {
-        const int kr = (lg >> 4) + (GT / 16) * (b0 + i);
-        const uint32_t w2[2] = {v[i].x, v[i].y};
+        const int kr = (lg >> 5) + (GT / 32) * (b0 + i);
         uint32_t o[4];
+        if constexpr (LAYOUT == kW4N) {
+          // halves of o[j]: values j and j+4 -> stored in the order (v0,v4,v1,v5,v2,v6,v3,v7)
 #pragma unroll
-        for (int j = 0; j < 8; j += 2) {
-          const float a = (float)(int8_t)(w2[j >> 2] >> (8 * (j & 3)));
-          const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
-          o[j >> 1] = add_mul2<XT>(X2<XT>::pack(a, b), of2[j >> 1], sc2[j >> 1], has_off);
+          for (int j = 0; j < 4; ++j)
+            o[j] = add_mul2<XT>(nibbles_to_x2<XT>(v[i].x >> (4 * j)), of2[j], sc2[j], has_off);
+        } else {
+          const uint32_t w2[2] = {v[i].x, v[i].y};
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            const float a = (float)(int8_t)(w2[j >> 2] >> (8 * (j & 3)));
+            const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
+            o[j >> 1] = add_mul2<XT>(X2<XT>::pack(a, b), of2[j >> 1], sc2[j >> 1], has_off);
+          }
         }
+        // MN-major operand: [64-channel block][8-k group][k row of 128 B][16-byte chunk ^ row]
         const uint32_t r = kr & 7;
-        *reinterpret_cast<uint4*>(a_tile + ng * 8192 + (kr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
+        *reinterpret_cast<uint4*>(b_tile + ng * 8192 + (kr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
             make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
   } else {
-    const uint32_t c = lg & 7;                         // 8-wide k chunk inside the 64-deep block
+    const uint32_t c = lg & 7;                               // 8-wide k chunk inside the 64-deep block
     const uint2* raw64 = reinterpret_cast<const uint2*>(raw);
 #pragma unroll
     for (int b0 = 0; b0 < ITEMS; b0 += BATCH) {
@@ -225,7 +283,7 @@ __device__ __forceinline__ void dequant_tile(const uint8_t* __restrict__ raw, ui
       uint32_t s2[BATCH], o2[BATCH];
 #pragma unroll
       for (int i = 0; i < BATCH; ++i) {
-        const int nr = (lg >> 3) + (GT / 8) * (b0 + i);    // channel row inside the tile
+        const int nr = (lg >> 3) + (GT / 8) * (b0 + i);      // channel row inside the tile
         const int64_t n = n_tile0 + nr;
         const bool nv = n < p.n;
         const float scv = nv ? X2<XT>::to_float(static_cast<const XT*>(p.scale)[g * p.n + n]) : 0.0f;
@@ -245,31 +303,31 @@ __device__ __forceinline__ void dequant_tile(const uint8_t* __restrict__ raw, ui
           const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
           o[j >> 1] = add_mul2<XT>(X2<XT>::pack(a, b), o2[i], s2[i], has_off);
         }
+        // K-major operand: [8-channel group][channel row of 128 B][16-byte chunk ^ row]
         const uint32_t r = nr & 7;
-        *reinterpret_cast<uint4*>(a_tile + (nr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
+        *reinterpret_cast<uint4*>(b_tile + (nr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
             make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
   }
 }
 
-template <int LAYOUT, typename XT, int BNX>
+template <int LAYOUT, typename XT, int MM, int NCH>
 __global__ void __launch_bounds__(kWqThreads, 1)
 wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const WqParams p) {
-  using C = WqCfg<LAYOUT, BNX>;
+  using C = WqCfg<LAYOUT, MM, NCH>;
   constexpr int LS = C::kLoadStages, AS = C::kASlots;
-  constexpr bool A_MN = LAYOUT != kW8K;
+  constexpr bool B_MN = LAYOUT != kW8K;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sA = smem + C::kAOff;
+  uint8_t* sB = smem + C::kBOff;
   uint8_t* sX = smem + C::kXOff;
   uint8_t* sRaw = smem + C::kRawOff;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::kBarOff);
-  uint64_t* lfree = full + LS;
-  uint64_t* aready = lfree + LS;
-  uint64_t* afree = aready + AS;
-  uint64_t* tfull = afree + AS;
+  uint64_t* done = full + LS;
+  uint64_t* aready = done + LS;
+  uint64_t* tfull = aready + AS;
   uint64_t* tempty = tfull + 1;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + C::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::kMiscOff + 4);
@@ -278,12 +336,9 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   if (threadIdx.x == 0) {
     for (int i = 0; i < LS; ++i) {
       mbar_init(&full[i], 1);
-      mbar_init(&lfree[i], 1);
+      mbar_init(&done[i], 1);
     }
-    for (int i = 0; i < AS; ++i) {
-      mbar_init(&aready[i], kWqDeqWarps / (LS > AS ? AS : 2));
-      mbar_init(&afree[i], 1);
-    }
+    for (int i = 0; i < AS; ++i) mbar_init(&aready[i], kWqDeqWarps / kWqGroups);
     mbar_init(tfull, 1);
     mbar_init(tempty, kWqDeqWarps);
     *abort_flag = 0;
@@ -303,124 +358,149 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
+      int it = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-        const int tn = u % p.tiles_n, mc = u / p.tiles_n;
-        for (int kb = 0; kb < p.kblocks; ++kb) {
-          if (!mbar_wait(&lfree[stage], phase ^ 1, abort_flag, kDevTimeoutProducer)) { ok = false; break; }
+      long long d_wait = 0, d_issue = 0;
+      (void)d_wait; (void)d_issue;
+      WQ_DIAG_BEGIN();
+      WqWalk walk(p, blockIdx.x, gridDim.x);
+      int unit, kb0, kb1;
+      while (ok && walk.next(unit, kb0, kb1)) {
+        const int tn = unit % p.tiles_n, mc = unit / p.tiles_n;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int stage = it % LS;
+          WQ_DIAG_ADD(d_issue);
+          if (!mbar_wait(&done[stage], (uint32_t)((it / LS) & 1) ^ 1u, abort_flag, kDevTimeoutProducer)) { ok = false; break; }
+          WQ_DIAG_ADD(d_wait);
           mbar_arrive_expect_tx(&full[stage], C::kRawBytes + C::kXBytes);
-          if (LAYOUT == kW4N)        // bytes of packed nibbles: 64 bytes = 128 channels per row of k
-            tma_load_2d(sRaw + stage * C::kRawBytes, &tmW, &full[stage], tn * 64, kb * kWqBK);
+          uint8_t* raw = sRaw + stage * C::kRawBytes;
+          if (LAYOUT == kW4N)        // bytes of packed nibbles: 128 bytes = 256 channels per row of k
+            tma_load_2d(raw, &tmW, &full[stage], tn * 128, kb * kWqBK);
           else if (LAYOUT == kW8N)
-            tma_load_2d(sRaw + stage * C::kRawBytes, &tmW, &full[stage], tn * kWqTileN, kb * kWqBK);
+            tma_load_2d(raw, &tmW, &full[stage], tn * kWqTileN, kb * kWqBK);
           else                       // k-contiguous: rows are channels
-            tma_load_2d(sRaw + stage * C::kRawBytes, &tmW, &full[stage], kb * kWqBK, tn * kWqTileN);
-          tma_load_2d(sX + stage * C::kXBytes, &tmX, &full[stage], kb * kWqBK, mc * BNX);
-          if (++stage == LS) { stage = 0; phase ^= 1; }
+            tma_load_2d(raw, &tmW, &full[stage], kb * kWqBK, tn * kWqTileN);
+#pragma unroll
+          for (int ch = 0; ch < NCH; ++ch)
+            tma_load_2d(sX + stage * C::kXBytes + ch * MM * 128, &tmX, &full[stage], kb * kWqBK, (mc * NCH + ch) * MM);
         }
       }
+      WQ_DIAG_STORE(0, d_wait);
+      WQ_DIAG_STORE(1, d_issue);
       if (!ok)
         for (int i = 0; i < 200; ++i) __nanosleep(1000);   // let copies in flight land before smem is released
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t fmt = sizeof(XT) == 2 && std::is_same<XT, __nv_bfloat16>::value ? 1u : 0u;
-      constexpr uint32_t idesc = make_idesc(1 /*f32*/, fmt, fmt, A_MN ? 1 : 0, 0, kWqTileN, BNX);
-      int stage = 0, slot = 0;
-      uint32_t phase = 0, aphase = 0, tphase = 0;
+      constexpr uint32_t fmt = std::is_same<XT, __nv_bfloat16>::value ? 1u : 0u;
+      constexpr uint32_t idesc = make_idesc(1 /*f32*/, fmt, fmt, 0, B_MN ? 1 : 0, MM, kWqTileN);
+      int it = 0;
+      uint32_t tphase = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+      long long d_tempty = 0, d_aready = 0, d_issue = 0;
+      (void)d_tempty; (void)d_aready; (void)d_issue;
+      const long long d_start = clock64();
+      (void)d_start;
+      WQ_DIAG_BEGIN();
+      WqWalk walk(p, blockIdx.x, gridDim.x);
+      int unit, kb0, kb1;
+      while (ok && walk.next(unit, kb0, kb1)) {
+        WQ_DIAG_ADD(d_issue);
         if (!mbar_wait(tempty, tphase ^ 1, abort_flag, kDevTimeoutMma)) { ok = false; break; }
+        WQ_DIAG_ADD(d_tempty);
         tc_fence_after();
-        for (int kb = 0; kb < p.kblocks; ++kb) {
-          if (!mbar_wait(&aready[slot], aphase, abort_flag, kDevTimeoutMma) ||
-              !mbar_wait(&full[stage], phase, abort_flag, kDevTimeoutMma)) { ok = false; break; }
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int stage = it % LS, slot = it % AS;
+          WQ_DIAG_ADD(d_issue);
+          if (!mbar_wait(&aready[slot], (uint32_t)(it / AS) & 1u, abort_flag, kDevTimeoutMma) ||
+              !mbar_wait(&full[stage], (uint32_t)(it / LS) & 1u, abort_flag, kDevTimeoutMma)) { ok = false; break; }
+          WQ_DIAG_ADD(d_aready);
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sA + slot * kWqABytes), b_addr = smem_u32(sX + stage * C::kXBytes);
+          const uint32_t a_addr = smem_u32(sX + stage * C::kXBytes), b_addr = smem_u32(sB + slot * kWqBBytes);
 #pragma unroll
           for (int k16 = 0; k16 < kWqBK / 16; ++k16) {
-            // MN-major A: 16 k = two 8-row groups of 1024 B; 64-channel groups 8192 B apart.
             // K-major A / B: 16 k = 32 bytes inside the 128-byte swizzle row; 8-row groups 1024 B apart.
-            const uint64_t adesc = A_MN ? make_smem_desc(a_addr + k16 * 2048, 8192, 1024, kSwizzle128B)
-                                        : make_smem_desc(a_addr + k16 * 32, 16, 1024, kSwizzle128B);
-            const uint64_t bdesc = make_smem_desc(b_addr + k16 * 32, 16, 1024, kSwizzle128B);
-#if !(defined(B200Q_DIAG) && (B200Q_DIAG & 2))
-            umma_f16(tmem_base, adesc, bdesc, idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
-#endif
+            // MN-major B: 16 k = two 8-row groups of 1024 B; 64-channel blocks 8192 B apart.
+            const uint64_t bdesc = B_MN ? make_smem_desc(b_addr + k16 * 2048, 8192, 1024, kSwizzle128B)
+                                        : make_smem_desc(b_addr + k16 * 32, 16, 1024, kSwizzle128B);
+#pragma unroll
+            for (int ch = 0; ch < NCH; ++ch) {
+              const uint64_t adesc = make_smem_desc(a_addr + ch * MM * 128 + k16 * 32, 16, 1024, kSwizzle128B);
+              umma_f16(tmem_base + ch * kWqTileN, adesc, bdesc, idesc, (kb > kb0 || k16 > 0) ? 1u : 0u);
+            }
           }
-          umma_commit(&afree[slot]);                     // operand slot may be overwritten ...
-          umma_commit(&lfree[stage]);                    // ... and the load stage refilled
-          if (++stage == LS) { stage = 0; phase ^= 1; }
-          if (++slot == AS) { slot = 0; aphase ^= 1; }
+          umma_commit(&done[stage]);                     // load stage and operand slot are free once these MMAs retire
         }
         if (!ok) break;
         umma_commit(tfull);
         tphase ^= 1;
       }
+      WQ_DIAG_ADD(d_issue);
+      WQ_DIAG_STORE(2, d_tempty);
+      WQ_DIAG_STORE(3, d_aready);
+      WQ_DIAG_STORE(4, d_issue);
+      WQ_DIAG_STORE(5, clock64() - d_start);
+      WQ_DIAG_STORE(9, it);
     }
   } else {
     // ------------------------------------------- dequantise, then epilogue
-    // The sixteen warps form G groups; group g owns every G-th K block, so G tiles are being
-    // dequantised at the same time and no warp waits for another inside a tile.  G stays below the
-    // number of load stages: a group must never wait for a phase of a `full` barrier while that
-    // barrier is still a whole phase behind (the parity test could not tell the two apart).
-    constexpr int G = LS > AS ? AS : 2;
-    constexpr int WG = kWqDeqWarps / G;                // warps per group
-    constexpr int GT = WG * 32;                        // threads per group
+    constexpr int GT = kWqGroupThreads;
     const int dw = warp - 2;                           // 0..15
-    const int group = dw / WG;
-    const int lg = (dw % WG) * 32 + lane;              // thread index inside the group
+    const int group = dw / (kWqDeqWarps / kWqGroups);
+    const int lg = (dw % (kWqDeqWarps / kWqGroups)) * 32 + lane;   // thread index inside the group
     const int quad = warp & 3;                         // TMEM lane quadrant of this warp
     const bool has_off = p.offset != nullptr;
-    int it_base = 0;                                   // K blocks this CTA has been through before this tile
+    int it_base = 0;                                   // K blocks this CTA has been through before this segment
     uint32_t tphase = 0;
     bool ok = true;
-    for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-      const int tn = u % p.tiles_n, mc = u / p.tiles_n;
+    long long d_wait = 0, d_work = 0, d_epi = 0;
+    (void)d_wait; (void)d_work; (void)d_epi;
+    WQ_DIAG_BEGIN();
+    WqWalk walk(p, blockIdx.x, gridDim.x);
+    int unit, kb0, kb1;
+    while (ok && walk.next(unit, kb0, kb1)) {
+      const int tn = unit % p.tiles_n, mc = unit / p.tiles_n;
       const int64_t n_tile0 = (int64_t)tn * kWqTileN;
       int64_t cur_group = -1;
       uint32_t sc2[4], of2[4];   // this thread's 8 channels as 16-bit pairs: kW4N (j, j+4), kW8N (2j, 2j+1)
       uint4 ns, no;              // parameters fetched ahead for the next K block of this group
-      const int64_t n_oct0 = n_tile0 + (lg & 15) * 8;
+      const int64_t n_oct0 = n_tile0 + (lg & 31) * 8;
       auto quant_group = [&](int kb) -> int64_t { return p.group_size > 0 ? ((int64_t)kb * kWqBK) / p.group_size : 0; };
-      int kb = (group - it_base % G + G) % G;          // first K block of this tile owned by the group
+      int kb = kb0 + ((group - it_base % kWqGroups + kWqGroups) % kWqGroups);   // first K block owned by the group
       int64_t g_next = quant_group(kb);
-      if (LAYOUT != kW8K && kb < p.kblocks) fetch_params8<XT>(p, g_next, n_oct0, ns, no);
-      for (; kb < p.kblocks; kb += G) {
-        const int it = it_base + kb;
-        const int stage = it % LS;
-        const uint32_t phase = (uint32_t)(it / LS) & 1u;
-        const int slot = it % AS;
-        const uint32_t aphase = (uint32_t)(it / AS) & 1u;
+      if (LAYOUT != kW8K && kb < kb1) fetch_params8<XT>(p, g_next, n_oct0, ns, no);
+      for (; kb < kb1; kb += kWqGroups) {
+        const int it = it_base + (kb - kb0);
+        const int stage = it % LS, slot = it % AS;
         const int64_t g = g_next;
         if (LAYOUT != kW8K) {
           if (g != cur_group) {
             cur_group = g;
             pair_params8<LAYOUT>(ns, no, sc2, of2);
           }
-          if (kb + G < p.kblocks) {                    // loads for the group's next K block fly during this one
-            g_next = quant_group(kb + G);
+          if (kb + kWqGroups < kb1) {                  // loads for the group's next K block fly during this one
+            g_next = quant_group(kb + kWqGroups);
             if (g_next != g) fetch_params8<XT>(p, g_next, n_oct0, ns, no);
           }
-        } else if (kb + G < p.kblocks) {
-          g_next = quant_group(kb + G);
+        } else if (kb + kWqGroups < kb1) {
+          g_next = quant_group(kb + kWqGroups);
         }
-        // warp-uniform decision, so that the warp stays converged for __syncwarp below
-        const bool got = __all_sync(0xffffffffu, mbar_wait(&full[stage], phase, abort_flag, kDevTimeoutEpilogue) &&
-                                                     mbar_wait(&afree[slot], aphase ^ 1, abort_flag, kDevTimeoutEpilogue));
-        if (!got) { ok = false; break; }
-#if !(defined(B200Q_DIAG) && (B200Q_DIAG & 1))
-        dequant_tile<LAYOUT, XT, GT>(sRaw + stage * C::kRawBytes, sA + slot * kWqABytes, lg, sc2, of2, has_off, p, g,
+        WQ_DIAG_ADD(d_work);
+        // The tile must have landed, and the MMAs that read this operand slot AS tiles ago must have retired.
+        bool got = mbar_wait(&full[stage], (uint32_t)(it / LS) & 1u, abort_flag, kDevTimeoutEpilogue);
+        if (got && it >= AS)
+          got = mbar_wait(&done[(it - AS) % LS], (uint32_t)((it - AS) / LS) & 1u, abort_flag, kDevTimeoutEpilogue);
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }   // warp-uniform, the warp stays converged
+        WQ_DIAG_ADD(d_wait);
+        dequant_tile<LAYOUT, XT, GT>(sRaw + stage * C::kRawBytes, sB + slot * kWqBBytes, lg, sc2, of2, has_off, p, g,
                                      n_tile0);
-#endif
         fence_proxy_async_smem();                      // generic-proxy stores -> visible to the MMA (async proxy)
         __syncwarp();
         if (lane == 0) mbar_arrive(&aready[slot]);
       }
-      it_base += p.kblocks;
+      it_base += kb1 - kb0;
+      WQ_DIAG_ADD(d_work);
       // The stop decision is taken by all dequantising warps together (named barrier 2).
       {
         bool got = ok && mbar_wait(tfull, tphase, abort_flag, kDevTimeoutEpilogue);
@@ -435,32 +515,73 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       }
       tc_fence_after();
       tphase ^= 1;
-      // -------- epilogue: rows are channels, columns are tokens; four warps share a lane quadrant
+      // -------- epilogue: accumulator rows are tokens, columns are channels; four warps share a lane quadrant.
+      // With M = 64 the rows sit in lanes 0-15 of each quadrant.
       {
-        constexpr int CH = BNX < 32 ? 16 : 32;
-        constexpr int kChunks = BNX / CH;
-        constexpr int kShare = kWqDeqWarps / 4;        // warps sharing one TMEM lane quadrant
-        const int share = dw >> 2;                     // this warp's slot among them
-        const int row = quad * 32 + lane;              // accumulator row = TMEM lane
-        const int64_t n = n_tile0 + (LAYOUT == kW4N ? w4_row_to_channel(row) : row);
-        const bool nv = n < p.n;
-        const float bias = (nv && p.bias) ? X2<XT>::to_float(static_cast<const XT*>(p.bias)[n]) : 0.0f;
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+        const int share = dw >> 2;                     // this warp's slot among the four of its quadrant
+        const int row = MM == 128 ? quad * 32 + lane : quad * 16 + lane;
+        const bool row_ok = MM == 128 || lane < 16;
+        const bool whole = (kb0 == 0 && kb1 == p.kblocks);
+        const int first = whole ? 0 : wq_cta_of_item((int64_t)unit * p.kblocks, p.total_items, (int)gridDim.x);
 #pragma unroll 1
-        for (int c = share; c < kChunks; c += kShare) {
-          uint32_t r[CH];
+        for (int cc = share; cc < NCH * (kWqTileN / 32); cc += 4) {
+          const int ch = cc / (kWqTileN / 32), c = cc % (kWqTileN / 32);
+          const int64_t token = ((int64_t)mc * NCH + ch) * MM + row;
+          const bool tv = row_ok && token < p.m;
+          float* part = whole ? nullptr : p.parts + ((int64_t)((int)blockIdx.x - first) * p.m + token) * p.n;
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + ch * kWqTileN;
+          uint32_t r[32];
           __syncwarp();
-          if constexpr (CH == 32) tmem_ld_x32(taddr + c * CH, r);
-          else tmem_ld_x16(taddr + c * CH, r);
+          tmem_ld_x32(taddr + c * 32, r);
           tmem_ld_wait();
-          if (nv) {
+          const int64_t n0 = n_tile0 + c * 32;
+          if (!tv || n0 >= p.n) continue;
+          const bool vec = n0 + 32 <= p.n;
+          if (!whole) {
+            // fp32 partial tile, channel order restored
+            if (vec) {
+              float4* dst = reinterpret_cast<float4*>(part + n0);
 #pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              const int64_t mm = (int64_t)mc * BNX + c * CH + j;
-              if (mm < p.m) {
-                float v = __uint_as_float(r[j]);
-                if (p.bias) v = __fadd_rn(v, bias);
-                static_cast<XT*>(p.out)[mm * p.n + n] = X2<XT>::from_float(v);
+              for (int q = 0; q < 8; ++q) {
+                float v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int o = 4 * q + j;
+                  v[j] = __uint_as_float(r[LAYOUT == kW4N ? w4_channel_to_column(o) : o]);
+                }
+                dst[q] = make_float4(v[0], v[1], v[2], v[3]);
+              }
+            } else {
+#pragma unroll
+              for (int o = 0; o < 32; ++o)
+                if (n0 + o < p.n) part[n0 + o] = __uint_as_float(r[LAYOUT == kW4N ? w4_channel_to_column(o) : o]);
+            }
+          } else {
+            XT* dst = static_cast<XT*>(p.out) + token * p.n + n0;
+            if (vec) {
+              uint32_t packed[16];
+#pragma unroll
+              for (int o = 0; o < 32; o += 2) {
+                float v0 = __uint_as_float(r[LAYOUT == kW4N ? w4_channel_to_column(o) : o]);
+                float v1 = __uint_as_float(r[LAYOUT == kW4N ? w4_channel_to_column(o + 1) : o + 1]);
+                if (p.bias) {
+                  v0 = __fadd_rn(v0, X2<XT>::to_float(static_cast<const XT*>(p.bias)[n0 + o]));
+                  v1 = __fadd_rn(v1, X2<XT>::to_float(static_cast<const XT*>(p.bias)[n0 + o + 1]));
+                }
+                packed[o >> 1] = X2<XT>::pack(v0, v1);
+              }
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                reinterpret_cast<uint4*>(dst)[q] =
+                    make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            } else {
+#pragma unroll
+              for (int o = 0; o < 32; ++o) {
+                if (n0 + o < p.n) {
+                  float v = __uint_as_float(r[LAYOUT == kW4N ? w4_channel_to_column(o) : o]);
+                  if (p.bias) v = __fadd_rn(v, X2<XT>::to_float(static_cast<const XT*>(p.bias)[n0 + o]));
+                  dst[o] = X2<XT>::from_float(v);
+                }
               }
             }
           }
@@ -469,6 +590,12 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty);
+      WQ_DIAG_ADD(d_epi);
+    }
+    if (threadIdx.x == 64) {
+      WQ_DIAG_STORE(6, d_wait);
+      WQ_DIAG_STORE(7, d_work);
+      WQ_DIAG_STORE(8, d_epi);
     }
   }
 
@@ -478,6 +605,24 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// stream-K: adds the fp32 partial tiles of every unit that was shared by several CTAs, in CTA
+// order, then bias and cast.  Units computed whole by one CTA were written by that CTA.
+template <typename XT>
+__global__ void wq_finalize_kernel(const WqParams p, int mm_rows) {
+  const int64_t total = p.m * p.n;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t token = i / p.n, n = i - token * p.n;
+    const int64_t unit = (token / mm_rows) * p.tiles_n + n / kWqTileN;
+    const int first = wq_cta_of_item(unit * p.kblocks, p.total_items, p.ctas);
+    const int last = wq_cta_of_item((unit + 1) * p.kblocks - 1, p.total_items, p.ctas);
+    if (last == first) continue;
+    float v = 0.0f;
+    for (int c = 0; c <= last - first; ++c) v = __fadd_rn(v, p.parts[((int64_t)c * p.m + token) * p.n + n]);
+    if (p.bias) v = __fadd_rn(v, X2<XT>::to_float(static_cast<const XT*>(p.bias)[n]));
+    static_cast<XT*>(p.out)[i] = X2<XT>::from_float(v);
   }
 }
 
@@ -510,10 +655,45 @@ __global__ void wq_simt_kernel(const XT* __restrict__ x, const void* __restrict_
   static_cast<XT*>(p.out)[mm * p.n + n] = X2<XT>::from_float(acc);
 }
 
-template <int LAYOUT, typename XT, int BNX>
+struct WqPlan {
+  int mm;            // tokens per unit: 64 (M = 64 MMAs), 128, or 256 (two M = 128 chunks sharing each weight tile)
+  int tiles_n, m_chunks, kblocks, units, ctas, stream_k, max_parts;
+  int64_t total_items;
+  size_t ws_bytes;
+};
+
+// Tiling and work split; shared by the workspace query and the launch.
+WqPlan wq_plan(int64_t m, int64_t k, int64_t n) {
+  WqPlan pl{};
+  pl.mm = m <= 64 ? 64 : m <= 128 ? 128 : 256;
+  pl.tiles_n = (int)ceil_div(n, kWqTileN);
+  pl.m_chunks = (int)ceil_div(m, pl.mm);
+  pl.kblocks = (int)ceil_div(k, kWqBK);
+  const int64_t units = (int64_t)pl.tiles_n * pl.m_chunks;
+  pl.units = (int)units;
+  pl.total_items = units * pl.kblocks;
+  const int sms = sm_count();
+  // Splitting K costs an fp32 partial tile per (CTA, tile) pair: worth it for very few tokens (measured: up to ~16), where the
+  // partials are small next to the weight stream, or when whole tiles would leave most SMs idle.
+  pl.stream_k = (pl.kblocks >= 2 && ((m <= 16 && units < 4LL * sms) || 2 * units < sms)) ? 1 : 0;
+  if (const char* env = getenv("B200Q_WQ_STREAMK")) pl.stream_k = (env[0] != '0' && pl.kblocks >= 2) ? 1 : 0;   // tuning override
+  pl.ctas = (int)(pl.stream_k ? (pl.total_items < sms ? pl.total_items : sms) : (units < sms ? units : sms));
+  pl.max_parts = 0;
+  if (pl.stream_k) {
+    for (int64_t u = 0; u < units; ++u) {
+      const int first = wq_cta_of_item(u * pl.kblocks, pl.total_items, pl.ctas);
+      const int last = wq_cta_of_item((u + 1) * pl.kblocks - 1, pl.total_items, pl.ctas);
+      if (last > first && last - first + 1 > pl.max_parts) pl.max_parts = last - first + 1;
+    }
+  }
+  pl.ws_bytes = (size_t)pl.max_parts * (size_t)m * (size_t)n * sizeof(float);
+  return pl;
+}
+
+template <int LAYOUT, typename XT, int MM, int NCH>
 int launch_wq(const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p, cudaStream_t st) {
-  using C = WqCfg<LAYOUT, BNX>;
-  auto kern = wq_umma_kernel<LAYOUT, XT, BNX>;
+  using C = WqCfg<LAYOUT, MM, NCH>;
+  auto kern = wq_umma_kernel<LAYOUT, XT, MM, NCH>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -523,36 +703,42 @@ int launch_wq(const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p,
       return fail(B200Q_ERR_LAUNCH, "weight_quant_matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(err));
     configured[dev] = true;
   }
-  const int grid = p.units < sm_count() ? p.units : sm_count();
-  kern<<<grid, kWqThreads, C::kDynamic, st>>>(tmW, tmX, p);
-  return check_launch("weight_quant_matmul (tcgen05)");
+  kern<<<p.ctas, kWqThreads, C::kDynamic, st>>>(tmW, tmX, p);
+  if (int rc = check_launch("weight_quant_matmul (tcgen05)")) return rc;
+  if (p.parts) {
+    const int64_t total = p.m * p.n;
+    const int64_t want = ceil_div(total, 256);
+    const int blocks = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
+    wq_finalize_kernel<XT><<<blocks, 256, 0, st>>>(p, MM * NCH);
+    return check_launch("weight_quant_matmul (stream-K sum)");
+  }
+  return B200Q_OK;
 }
 
 template <int LAYOUT, typename XT>
-int dispatch_bnx(int bnx, const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p, cudaStream_t st) {
-  switch (bnx) {
-    case 16: return launch_wq<LAYOUT, XT, 16>(tmW, tmX, p, st);
-    case 32: return launch_wq<LAYOUT, XT, 32>(tmW, tmX, p, st);
-    case 64: return launch_wq<LAYOUT, XT, 64>(tmW, tmX, p, st);
-    case 128: return launch_wq<LAYOUT, XT, 128>(tmW, tmX, p, st);
-    default: return launch_wq<LAYOUT, XT, 256>(tmW, tmX, p, st);
-  }
+int dispatch_mm(int mm, const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p, cudaStream_t st) {
+  if (mm == 64) return launch_wq<LAYOUT, XT, 64, 1>(tmW, tmX, p, st);
+  if (mm == 128) return launch_wq<LAYOUT, XT, 128, 1>(tmW, tmX, p, st);
+  return launch_wq<LAYOUT, XT, 128, 2>(tmW, tmX, p, st);     // mm == 256: two 128-token chunks per weight tile
 }
 
 template <typename XT>
-int dispatch_layout(int layout, int bnx, const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p,
+int dispatch_layout(int layout, int mm, const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p,
                     cudaStream_t st) {
   switch (layout) {
-    case kW4N: return dispatch_bnx<kW4N, XT>(bnx, tmW, tmX, p, st);
-    case kW8N: return dispatch_bnx<kW8N, XT>(bnx, tmW, tmX, p, st);
-    default: return dispatch_bnx<kW8K, XT>(bnx, tmW, tmX, p, st);
+    case kW4N: return dispatch_mm<kW4N, XT>(mm, tmW, tmX, p, st);
+    case kW8N: return dispatch_mm<kW8N, XT>(mm, tmW, tmX, p, st);
+    default: return dispatch_mm<kW8K, XT>(mm, tmW, tmX, p, st);
   }
 }
 
 }  // namespace
 }  // namespace b200q
 
-extern "C" size_t b200q_weight_quant_matmul_workspace_bytes(int64_t, int64_t, int64_t, int) { return 0; }
+extern "C" size_t b200q_weight_quant_matmul_workspace_bytes(int64_t m, int64_t k, int64_t n, int /*weight_bits*/) {
+  if (m <= 0 || k <= 0 || n <= 0) return 0;
+  return b200q::wq_plan(m, k, n).ws_bytes;
+}
 
 extern "C" int b200q_weight_quant_matmul(const b200q_weight_quant_matmul_args* a, void* stream) {
   using namespace b200q;
@@ -586,9 +772,10 @@ extern "C" int b200q_weight_quant_matmul(const b200q_weight_quant_matmul_args* a
     layout = kW8K;
   }
   const bool fused = layout >= 0 && a->k >= 8 && a->k % 8 == 0 && a->n % 8 == 0 && aligned(a->x, 16) &&
-                     aligned(a->weight, 16) && aligned(a->antiquant_scale, 16) &&
+                     aligned(a->weight, 16) && aligned(a->antiquant_scale, 16) && aligned(a->out, 16) &&
                      (a->antiquant_offset == nullptr || aligned(a->antiquant_offset, 16)) &&
-                     (a->group_size == 0 || a->group_size % kWqBK == 0) && a->k < (1LL << 31) && a->n < (1LL << 31);
+                     (a->group_size == 0 || a->group_size % kWqBK == 0) && a->k < (1LL << 31) && a->n < (1LL << 31) &&
+                     a->m < (1LL << 31);
   if (!fused) {
     dim3 block(32, 8), grid((unsigned)ceil_div(a->n, 32), (unsigned)ceil_div(a->m, 8));
     B200Q_REQUIRE(grid.y <= 65535, B200Q_ERR_UNSUPPORTED,
@@ -602,18 +789,23 @@ extern "C" int b200q_weight_quant_matmul(const b200q_weight_quant_matmul_args* a
     return check_launch("weight_quant_matmul (simt)");
   }
 
-  const int bnx = a->m <= 16 ? 16 : a->m <= 32 ? 32 : a->m <= 64 ? 64 : a->m <= 128 ? 128 : 256;
-  p.tiles_n = (int)ceil_div(a->n, kWqTileN);
-  p.m_chunks = (int)ceil_div(a->m, bnx);
-  p.kblocks = (int)ceil_div(a->k, kWqBK);
-  const int64_t units = (int64_t)p.tiles_n * p.m_chunks;
-  B200Q_REQUIRE(units < (1LL << 31), B200Q_ERR_UNSUPPORTED, "weight_quant_matmul: too many tiles");
-  p.units = (int)units;
+  const WqPlan pl = wq_plan(a->m, a->k, a->n);
+  B200Q_REQUIRE(pl.total_items < (1LL << 40) && (int64_t)pl.tiles_n * pl.m_chunks < (1LL << 31), B200Q_ERR_UNSUPPORTED,
+                "weight_quant_matmul: too many tiles");
+  p.tiles_n = pl.tiles_n; p.m_chunks = pl.m_chunks; p.kblocks = pl.kblocks; p.units = pl.units;
+  p.total_items = pl.total_items; p.stream_k = pl.stream_k; p.ctas = pl.ctas;
+  p.parts = nullptr;
+  if (pl.ws_bytes) {
+    B200Q_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= pl.ws_bytes && aligned(a->workspace, 256),
+                  B200Q_ERR_WORKSPACE, "weight_quant_matmul: needs %zu bytes of 256-byte aligned workspace, got %zu",
+                  pl.ws_bytes, a->workspace_bytes);
+    p.parts = static_cast<float*>(a->workspace);
+  }
 
   CUtensorMap tmW, tmX;
   int rc;
   if (layout == kW4N)
-    rc = make_tmap_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->weight, a->n / 2, a->k, a->n / 2, 64, kWqBK,
+    rc = make_tmap_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->weight, a->n / 2, a->k, a->n / 2, 128, kWqBK,
                       CU_TENSOR_MAP_SWIZZLE_NONE, "weight_quant_matmul (int4 weight)");
   else if (layout == kW8N)
     rc = make_tmap_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->weight, a->n, a->k, a->w_stride_k, kWqTileN, kWqBK,
@@ -623,9 +815,15 @@ extern "C" int b200q_weight_quant_matmul(const b200q_weight_quant_matmul_args* a
                       CU_TENSOR_MAP_SWIZZLE_NONE, "weight_quant_matmul (int8 weight)");
   if (rc) return rc;
   rc = make_tmap_2d(&tmX, a->x_dtype == B200Q_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                    2, a->x, a->k, a->m, a->k * 2, kWqBK, bnx, CU_TENSOR_MAP_SWIZZLE_128B,
+                    2, a->x, a->k, a->m, a->k * 2, kWqBK, pl.mm == 64 ? 64 : 128, CU_TENSOR_MAP_SWIZZLE_128B,
                     "weight_quant_matmul (activations)");
   if (rc) return rc;
-  if (a->x_dtype == B200Q_BF16) return dispatch_layout<__nv_bfloat16>(layout, bnx, tmW, tmX, p, st);
-  return dispatch_layout<__half>(layout, bnx, tmW, tmX, p, st);
+  if (a->x_dtype == B200Q_BF16) return dispatch_layout<__nv_bfloat16>(layout, pl.mm, tmW, tmX, p, st);
+  return dispatch_layout<__half>(layout, pl.mm, tmW, tmX, p, st);
 }
+
+#ifdef B200Q_DIAG_TIMING
+extern "C" int b200q_diag_read(unsigned long long* out16) {
+  return cudaMemcpyFromSymbol(out16, b200q::g_wq_diag, sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : 3;
+}
+#endif

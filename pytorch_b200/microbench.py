@@ -103,6 +103,7 @@ def bench_w4(m, k, n, gs, iters, plain):
     of = (torch.rand(groups, n, device="cuda") * 2 - 1).to(torch.bfloat16)
     x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
     out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    ws = torch.empty(max(1, lib.b200q_weight_quant_matmul_workspace_bytes(m, k, n, 4)), dtype=torch.uint8, device="cuda")
     args = []
     for pk in packs:
         a = cabi.WeightQuantMatmulArgs()
@@ -110,6 +111,7 @@ def bench_w4(m, k, n, gs, iters, plain):
         a.m, a.k, a.n = m, k, n
         a.antiquant_scale, a.antiquant_offset, a.group_size = sc.data_ptr(), of.data_ptr(), gs
         a.out = out.data_ptr()
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
         args.append(a)
     calls = [(lambda sp, a=a: cabi.check(lib.b200q_weight_quant_matmul(C.byref(a), sp))) for a in args]
     ms = _graph_time(calls, iters, plain)
