@@ -135,8 +135,31 @@ def run_b200(args):
     ops = torch.ops.npu
     d = make_inputs(rank, world, device)
     w_gu_t, w_dn_t = d["w_gu"].t(), d["w_dn"].t()
-    gat_gu = sharded.ColumnShardedOutput(M, 2 * FFN, torch.bfloat16, device)
-    gat_dn = sharded.ColumnShardedOutput(M, HIDDEN, torch.bfloat16, device)
+    exchange = "none"
+    if world > 1:
+        # Preferred exchange: GEMM writes its column block into a peer-mapped [M, N] matrix and
+        # b200q_scatter_columns pushes it to the peers over NVLink.  NCCL all-gather + re-interleave copy
+        # is used only where symmetric memory cannot be set up (BENCH_EXCHANGE=nccl forces it).
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        try:
+            if os.environ.get("BENCH_EXCHANGE", "p2p") != "p2p":
+                raise RuntimeError("NCCL exchange requested")
+            gat_gu = sharded.PeerColumnGather(M, 2 * FFN, torch.bfloat16, device)
+            gat_dn = sharded.PeerColumnGather(M, HIDDEN, torch.bfloat16, device)
+            exchange = "p2p_scatter"
+        except Exception as exc:                                   # noqa: BLE001
+            if rank == 0:
+                print(f"[bench] peer-memory exchange unavailable ({exc}); using NCCL all-gather", file=sys.stderr)
+            gat_gu = sharded.ColumnShardedOutput(M, 2 * FFN, torch.bfloat16, device)
+            gat_dn = sharded.ColumnShardedOutput(M, HIDDEN, torch.bfloat16, device)
+            exchange = "nccl_all_gather"
+        flag = torch.tensor([1 if exchange == "p2p_scatter" else 0], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)                # all ranks must agree
+        if int(flag.item()) == 0 and exchange == "p2p_scatter":
+            gat_gu = sharded.ColumnShardedOutput(M, 2 * FFN, torch.bfloat16, device)
+            gat_dn = sharded.ColumnShardedOutput(M, HIDDEN, torch.bfloat16, device)
+            exchange = "nccl_all_gather"
+    from pytorch_b200 import _cabi
     gemm_events, dq_events = [], []
 
     def ev():
@@ -144,14 +167,21 @@ def run_b200(args):
 
     comm = torch.cuda.Stream(device=device) if world > 1 else None
 
+    def gemm(q, w_t, scale, s, gat):
+        if exchange == "p2p_scatter":      # C-ABI call with the output placed inside the peer-mapped matrix
+            return _cabi.quant_matmul(q, w_t, scale, pertoken_scale=s, output_dtype=torch.bfloat16, out=gat.local_block())
+        return ops.npu_quant_matmul(q, w_t, scale, pertoken_scale=s, output_dtype=torch.bfloat16)
+
     def gather_async(gat, y):
-        """All-gather on the side stream so that it overlaps the next GEMM (independent data)."""
+        """Exchange on the side stream so that it overlaps the next GEMM (independent data)."""
         if world == 1:
             return y
         main = torch.cuda.current_stream()
         comm.wait_stream(main)
-        y.record_stream(comm)
         with torch.cuda.stream(comm):
+            if exchange == "p2p_scatter":
+                return gat.gather()
+            y.record_stream(comm)
             return gat.gather(y)
 
     def step(x, x_down, record=False):
@@ -159,13 +189,13 @@ def run_b200(args):
         if record: e[0].record()
         q, s = ops.npu_dynamic_quant(x, smooth_scales=d["smooth"])
         if record: e[1].record()
-        y1 = ops.npu_quant_matmul(q, w_gu_t, d["s_gu"], pertoken_scale=s, output_dtype=torch.bfloat16)
+        y1 = gemm(q, w_gu_t, d["s_gu"], s, gat_gu if world > 1 else None)
         if record: e[2].record()
         o1 = gather_async(gat_gu, y1)
         if record: e[3].record()
         q2, s2 = ops.npu_dynamic_quant(x_down, smooth_scales=d["smooth_down"])
         if record: e[4].record()
-        y2 = ops.npu_quant_matmul(q2, w_dn_t, d["s_dn"], pertoken_scale=s2, output_dtype=torch.bfloat16)
+        y2 = gemm(q2, w_dn_t, d["s_dn"], s2, gat_dn if world > 1 else None)
         if record: e[5].record()
         o2 = gather_async(gat_dn, y2)
         if world > 1:
@@ -249,7 +279,7 @@ def run_b200(args):
                    "l2": "weights streamed per step (705 MB / N per rank) exceed the 126 MB L2; no explicit flush"},
         "clocks": clocks,
         "e2e": e2e,
-        "gpu_launches": 4 * args.steps,
+        "gpu_launches": (4 if world == 1 else 6 if exchange == "p2p_scatter" else 4) * args.steps,
         "roofline": {"bound": "tensor", "kernel": "w8a8_umma_pair_kernel", "achieved": round(gemm_flops_per_launch / (gemm_ms * 1e-3) / 1e12, 1),
                      "peak": round(int8_peak, 1), "unit": "TOP/s", "frac": round(gemm_flops_per_launch / (gemm_ms * 1e-3) / 1e12 / int8_peak, 4),
                      "traffic": None,
@@ -269,8 +299,11 @@ def run_b200(args):
         out["exposed_gather_ms_per_step"] = round(ms_step - compute_ms, 4)
         recv = (world - 1) / world * (M * 2 * FFN + M * HIDDEN) * 2
         out["gather_link_floor_ms"] = round(recv / 770e9 * 1e3, 4)
-        out["gather_note"] = ("all_gather_into_tensor over NVLink plus one re-interleave copy per projection, on a side "
-                              "stream; link floor = bytes each GPU must receive / 770 GB/s measured peer bandwidth")
+        out["exchange"] = exchange
+        out["gather_note"] = ("p2p_scatter: the GEMM writes its column block into a peer-mapped [M,N] matrix and "
+                              "b200q_scatter_columns pushes it to every peer with 128-bit stores over NVLink, then a "
+                              "device-side barrier; nccl_all_gather: all_gather_into_tensor plus one re-interleave copy. "
+                              "Either runs on a side stream. link floor = bytes each GPU must receive / 770 GB/s")
     if rank == 0 and world == 1:
         out["c2_linears_m2048"] = bench_c2(ops, device, int8_peak)
         out["cpu_baseline"] = cpu_baseline(d, sample_rows=256)

@@ -79,10 +79,12 @@ typedef struct {
   const void* bias;        /* [n] or NULL; i32 joins the accumulator, bf16/f16/f32 are added
                               after the scales                                                */
   int bias_dtype;
-  void* out;               /* [m,n], row stride n                                             */
+  void* out;               /* [m,n], row stride out_row_stride (n when that field is 0)       */
   int out_dtype;           /* B200Q_I8, B200Q_F16, B200Q_BF16 or B200Q_I32                    */
   void* workspace;         /* >= b200q_quant_matmul_workspace_bytes(), 256-byte aligned       */
   size_t workspace_bytes;
+  int64_t out_row_stride;  /* elements between rows of out; 0 means n.  A larger stride lets a
+                              column shard be written straight into its place in an [m, N] matrix */
 } b200q_quant_matmul_args;
 
 size_t b200q_quant_matmul_workspace_bytes(int64_t m, int64_t k, int64_t n, int64_t x2_stride_k,
@@ -140,6 +142,16 @@ int b200q_weight_quant_matmul(const b200q_weight_quant_matmul_args* args, void* 
  *   The operator does not occur in the reference tree; the nibble order is the one its
  *   unpack helper expects, test/custom_ops/test_npu_anti_quant.py:12-24. */
 int b200q_int4pack(const int32_t* w, int32_t* packed, int64_t rows, int64_t cols, void* stream);
+
+/* Exchange step of the column-sharded linear: pushes bytes [col_offset, col_offset + block_bytes) of
+ * every row of the local [rows, row_stride_bytes] matrix `src` to the same place in each of the
+ * `n_peers` matrices `peer_dst[i]` (HOST array of device pointers into peers' memory, mapped for
+ * peer access by the caller, e.g. through CUDA IPC or torch symmetric memory).  Plain 128-bit stores
+ * over NVLink; the caller runs a cross-rank barrier afterwards.
+ *   replaces hcclAllGather in ProcessGroupHCCL::_allgather_base
+ *   (torch_npu/csrc/distributed/ProcessGroupHCCL.cpp:5896-5956) for this path. */
+int b200q_scatter_columns(const void* src, void* const* peer_dst, int n_peers, int64_t rows,
+                          int64_t row_stride_bytes, int64_t col_offset_bytes, int64_t block_bytes, void* stream);
 
 /* npu_trans_quant_param(scale, offset=None): fp32 scale -> int64 dequant parameter
  *   (torch_npu/contrib/module/linear_quant.py:107-108; contract test/test_fake_tensor.py:1929-1943).

@@ -25,7 +25,7 @@ EXPORTS = (
     "b200q_dynamic_quant", "b200q_quant_matmul_workspace_bytes", "b200q_quant_matmul",
     "b200q_static_scratch_bytes", "b200q_quant_matmul_static_scratch",
     "b200q_weight_quant_matmul_workspace_bytes", "b200q_weight_quant_matmul", "b200q_int4pack",
-    "b200q_trans_quant_param",
+    "b200q_trans_quant_param", "b200q_scatter_columns",
 )
 
 
@@ -40,6 +40,7 @@ class QuantMatmulArgs(C.Structure):
         ("bias", C.c_void_p), ("bias_dtype", C.c_int),
         ("out", C.c_void_p), ("out_dtype", C.c_int),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("out_row_stride", C.c_int64),
     ]
 
 
@@ -92,6 +93,8 @@ def lib() -> C.CDLL:
         l.b200q_weight_quant_matmul.argtypes = [C.POINTER(WeightQuantMatmulArgs), C.c_void_p]
         l.b200q_int4pack.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
         l.b200q_trans_quant_param.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p]
+        l.b200q_scatter_columns.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int64, C.c_int64, C.c_int64,
+                                            C.c_int64, C.c_void_p]
         _lib = l
     return _lib
 
@@ -171,6 +174,8 @@ def quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None, 
         b = bias.contiguous(); keep.append(b)
         a.bias, a.bias_dtype = b.data_ptr(), DTYPE.get(b.dtype, 99)
     a.out, a.out_dtype = out.data_ptr(), DTYPE.get(out_dtype, 99)
+    if out.dim() >= 2 and out.stride(-1) == 1 and out.stride(-2) != n and m > 1:
+        a.out_row_stride = out.stride(-2)      # a column slice of a wider matrix
     if static_scratch:
         check(lib().b200q_quant_matmul_static_scratch(C.byref(a), _stream()))
         return out
@@ -233,3 +238,15 @@ def trans_quant_param(scale: torch.Tensor, out_shape) -> torch.Tensor:
     out = torch.empty(tuple(out_shape), dtype=torch.int64, device=scale.device)
     check(lib().b200q_trans_quant_param(_ptr(sc), sc.numel(), _ptr(out), out.numel(), _stream()))
     return out
+
+
+def scatter_columns(full: torch.Tensor, peer_ptrs, col_lo: int, col_hi: int) -> None:
+    """Pushes columns [col_lo, col_hi) of the local row-major matrix ``full`` to the same place in the
+    matrices at the device addresses ``peer_ptrs`` (peers' copies of ``full``, mapped for peer access)."""
+    _need_cuda(full)
+    if full.dim() != 2 or not full.is_contiguous():
+        raise B200QError(ERR_BAD_ARG, "scatter_columns: a contiguous 2-D matrix is required")
+    es = full.element_size()
+    arr = (C.c_void_p * max(len(peer_ptrs), 1))(*[C.c_void_p(int(p)) for p in peer_ptrs])
+    check(lib().b200q_scatter_columns(_ptr(full), arr, len(peer_ptrs), full.shape[0], full.shape[1] * es,
+                                      col_lo * es, (col_hi - col_lo) * es, _stream()))

@@ -6,3 +6,4 @@
 #include "int4pack.cu"
 #include "w8a8_gemm.cu"
 #include "w4a16_gemm.cu"
+#include "peer_scatter.cu"

@@ -48,6 +48,7 @@ struct Epi {
   void* out;
   int32_t* acc_ws;  // split-K: raw accumulators are added here instead of writing `out`
   int64_t m, n;
+  int64_t ldo;      // row stride of `out` in elements (>= n)
   int scale_dtype, scale_bcast, offset_bcast, bias_dtype, out_dtype;
   uint32_t flags;
 };
@@ -148,7 +149,7 @@ __device__ __forceinline__ void store_token_rows(const Epi& e, uint32_t taddr, i
     } else if (vec && n0 + CH <= e.n) {
       // 128-bit stores
       if (e.out_dtype == B200Q_I32) {
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<int*>(e.out) + mm * e.n + n0);
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<int*>(e.out) + mm * e.ldo + n0);
 #pragma unroll
         for (int q = 0; q < CH / 4; ++q)
           dst[q] = make_uint4(r[4 * q] + col_i[c * CH + 4 * q], r[4 * q + 1] + col_i[c * CH + 4 * q + 1],
@@ -166,7 +167,7 @@ __device__ __forceinline__ void store_token_rows(const Epi& e, uint32_t taddr, i
           }
           packed[j / 4] = w;
         }
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<int8_t*>(e.out) + mm * e.n + n0);
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<int8_t*>(e.out) + mm * e.ldo + n0);
 #pragma unroll
         for (int q = 0; q < CH / 16; ++q)
           dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
@@ -180,7 +181,7 @@ __device__ __forceinline__ void store_token_rows(const Epi& e, uint32_t taddr, i
               dequant((int)r[j + 1], col_i[cj + 1], col_f0[cj + 1], pt, col_f2[cj + 1], col_f1[cj + 1], e.flags);
           packed[j / 2] = to_bits16(v0, e.out_dtype) | (to_bits16(v1, e.out_dtype) << 16);
         }
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned short*>(e.out) + mm * e.n + n0);
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned short*>(e.out) + mm * e.ldo + n0);
 #pragma unroll
         for (int q = 0; q < CH / 8; ++q)
           dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
@@ -191,7 +192,7 @@ __device__ __forceinline__ void store_token_rows(const Epi& e, uint32_t taddr, i
         if (n0 + j < e.n) {
           const int cj = c * CH + j;
           const int acc = (int)r[j];
-          store_one(e, mm * e.n + n0 + j, acc, col_i[cj],
+          store_one(e, mm * e.ldo + n0 + j, acc, col_i[cj],
                     dequant(acc, col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags));
         }
       }
@@ -375,7 +376,7 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (e.acc_ws) {
                   atomicAdd(e.acc_ws + mm * e.n + n, acc);
                 } else {
-                  store_one(e, mm * e.n + n, acc, ib, dequant(acc, ib, sc, col_f0[c * CH + j], fb, off, e.flags));
+                  store_one(e, mm * e.ldo + n, acc, ib, dequant(acc, ib, sc, col_f0[c * CH + j], fb, off, e.flags));
                 }
               }
             }
@@ -567,7 +568,7 @@ __global__ void splitk_finalize_kernel(const int32_t* __restrict__ acc, const Ep
     const int64_t mm = i / e.n, n = i - mm * e.n;
     const int a = acc[i], ib = load_int_bias(e, n);
     const float pt = (e.flags & kHasPt) ? __ldg(e.pertoken + mm) : 1.0f;
-    store_one(e, i, a, ib, dequant(a, ib, load_scale(e, n), pt, load_float_bias(e, n), load_offset(e, n), e.flags));
+    store_one(e, mm * e.ldo + n, a, ib, dequant(a, ib, load_scale(e, n), pt, load_float_bias(e, n), load_offset(e, n), e.flags));
   }
 }
 
@@ -584,7 +585,7 @@ __global__ void w8a8_simt_kernel(const int8_t* __restrict__ x1, const int8_t* __
   for (int64_t i = 0; i < k; ++i) acc += (int)a[i] * (int)b[i * sk];
   const int ib = load_int_bias(e, n);
   const float pt = (e.flags & kHasPt) ? __ldg(e.pertoken + mm) : 1.0f;
-  store_one(e, mm * e.n + n, acc, ib,
+  store_one(e, mm * e.ldo + n, acc, ib,
             dequant(acc, ib, load_scale(e, n), pt, load_float_bias(e, n), load_offset(e, n), e.flags));
 }
 
@@ -750,6 +751,8 @@ extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream
   B200Q_REQUIRE(a->bias == nullptr || a->bias_dtype == B200Q_I32 || a->bias_dtype == B200Q_BF16 ||
                     a->bias_dtype == B200Q_F16 || a->bias_dtype == B200Q_F32,
                 B200Q_ERR_UNSUPPORTED, "quant_matmul: bias must be i32, bf16, f16 or f32");
+  B200Q_REQUIRE(a->out_row_stride == 0 || a->out_row_stride >= a->n, B200Q_ERR_BAD_ARG,
+                "quant_matmul: out_row_stride (%lld) is smaller than n (%lld)", (long long)a->out_row_stride, (long long)a->n);
   B200Q_REQUIRE(!(a->out_dtype == B200Q_I32 && a->bias != nullptr && a->bias_dtype != B200Q_I32), B200Q_ERR_UNSUPPORTED,
                 "quant_matmul: int32 output takes an int32 bias only");
 
@@ -757,13 +760,14 @@ extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream
   Epi e{};
   e.scale = a->scale; e.offset = a->offset; e.pertoken = a->pertoken_scale; e.bias = a->bias; e.out = a->out;
   e.acc_ws = nullptr; e.m = a->m; e.n = a->n;
+  e.ldo = a->out_row_stride > 0 ? a->out_row_stride : a->n;
   e.scale_dtype = a->scale_dtype; e.scale_bcast = a->scale_len == 1; e.offset_bcast = a->offset_len == 1;
   e.bias_dtype = a->bias ? a->bias_dtype : B200Q_NONE; e.out_dtype = a->out_dtype;
   e.flags = (a->pertoken_scale ? kHasPt : 0u) | (a->offset ? kHasOff : 0u) |
             (a->bias ? (a->bias_dtype == B200Q_I32 ? kHasIntBias : kHasFloatBias) : 0u);
   {
     const int64_t ob = a->out_dtype == B200Q_I8 ? 1 : a->out_dtype == B200Q_I32 ? 4 : 2;
-    if (aligned(a->out, 16) && (a->n * ob) % 16 == 0) e.flags |= kOutVec;
+    if (aligned(a->out, 16) && (e.ldo * ob) % 16 == 0) e.flags |= kOutVec;
   }
 
   Plan p = make_plan(a->m, a->k, a->n, a->x2_stride_k, a->x2_stride_n, a->x1, a->x2);

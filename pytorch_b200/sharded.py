@@ -55,6 +55,40 @@ class ColumnShardedOutput:
         return self.full
 
 
+class PeerColumnGather:
+    """The same exchange without NCCL and without the re-interleave copy: every rank keeps its
+    ``[M, N]`` result in symmetric (peer-mapped) memory, the GEMM writes the rank's column block
+    straight into the local matrix (``out_row_stride = N``), ``b200q_scatter_columns`` pushes that
+    block into every peer's matrix over NVLink with plain 128-bit stores, and a device-side barrier
+    on the symmetric-memory signal pads tells every rank that all blocks have landed.
+
+    Usage per step: ``y = self.local_block()`` (a ``[M, N/g]`` view to hand to the GEMM as ``out``),
+    then ``full = self.gather()``.  ``full`` is overwritten by the next step's pushes: finish reading
+    it (or copy it) before any rank starts that step.  No rank may leave while a step is in flight."""
+
+    def __init__(self, m: int, n: int, dtype: torch.dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = dist.group.WORLD if group is None else group
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.m, self.n = m, n
+        self.lo, self.hi = shard_bounds(n, self.rank, self.world)
+        self.full = symm_mem.empty((m, n), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.full, self.group)
+        ptrs = list(self.handle.buffer_ptrs)
+        # staggered order: rank r starts with r+1, so the switch sees an all-to-all, not a hot spot
+        self.peer_ptrs = [ptrs[(self.rank + 1 + i) % self.world] for i in range(self.world - 1)]
+
+    def local_block(self) -> torch.Tensor:
+        return self.full[:, self.lo:self.hi]
+
+    def gather(self) -> torch.Tensor:
+        from . import _cabi
+        _cabi.scatter_columns(self.full, self.peer_ptrs, self.lo, self.hi)
+        self.handle.barrier(channel=0)
+        return self.full
+
+
 def sharded_w8a8_linear(x: torch.Tensor, smooth_scales, weight_nk_shard: torch.Tensor, scale_shard: torch.Tensor,
                         gather: ColumnShardedOutput, *, output_dtype=torch.bfloat16, quantized=None):
     """dynamic quant (replicated) -> W8A8 GEMM on this rank's columns -> all-gather along N.

@@ -34,7 +34,7 @@ def test_cabi_exports_every_declared_symbol():
 
 def test_struct_layout_matches_header():
     from pytorch_b200 import _cabi
-    assert ctypes.sizeof(_cabi.QuantMatmulArgs) == 19 * 8
+    assert ctypes.sizeof(_cabi.QuantMatmulArgs) == 20 * 8
     assert ctypes.sizeof(_cabi.WeightQuantMatmulArgs) == 16 * 8
 
 

@@ -1,0 +1,101 @@
+"""GPU side of the column-sharded linear: writing a shard into its place of a wider matrix
+(out_row_stride) and the peer push kernel, emulated on one GPU with several local buffers standing in
+for the peers' matrices; on a box with two or more GPUs also the real two-rank exchange over
+symmetric memory, checked against the unsharded oracle."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+from oracle import quant_oracle as oracle
+from pytorch_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def cabi():
+    from pytorch_b200 import _cabi
+    _cabi.lib()
+    assert torch.cuda.is_available()
+    return _cabi
+
+
+@pytest.mark.parametrize("m", [16, 640])
+def test_shards_written_in_place_and_pushed(cabi, m):
+    world, k, n = 4, 512, 1024
+    d = workloads.w8a8_linear(m, k, n, 321)
+    q, s = oracle.dynamic_quant(d["x"], d["smooth_scales"])
+    want = oracle.quant_matmul(q, d["x2"], d["scale"], pertoken_scale=s, output_dtype=torch.bfloat16)
+    qd, sd = q.cuda(), s.cuda()
+    fulls = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    per = n // world
+    for r in range(world):                               # "rank" r computes its columns into its own matrix
+        w = d["weight_nk"][r * per:(r + 1) * per].cuda()
+        view = fulls[r][:, r * per:(r + 1) * per]
+        out = cabi.quant_matmul(qd, w.t(), d["scale"][r * per:(r + 1) * per].cuda(), pertoken_scale=sd,
+                                output_dtype=torch.bfloat16, out=view)
+        assert out.data_ptr() == view.data_ptr()
+        assert torch.isnan(fulls[r][:, :r * per].float()).all() and torch.isnan(fulls[r][:, (r + 1) * per:].float()).all()
+    for r in range(world):                               # ... and pushes them to the other three
+        peers = [fulls[(r + 1 + i) % world].data_ptr() for i in range(world - 1)]
+        cabi.scatter_columns(fulls[r], peers, r * per, (r + 1) * per)
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert torch.equal(fulls[r].cpu().view(torch.int16), want.view(torch.int16))
+    with pytest.raises(cabi.B200QError):
+        cabi.scatter_columns(fulls[0], [fulls[1].data_ptr()], 4, 4 + 3)      # 6-byte block: not a 16-byte multiple
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, results):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TORCH_SYMM_MEM_DISABLE_MULTICAST="1",
+                      NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    from pytorch_b200 import _cabi, sharded
+    try:
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        m, k, n = 256, 1024, 2048
+        d = workloads.w8a8_linear(m, k, n, 77)
+        q, s = oracle.dynamic_quant(d["x"], d["smooth_scales"])
+        want = oracle.quant_matmul(q, d["x2"], d["scale"], pertoken_scale=s, output_dtype=torch.bfloat16)
+        gat = sharded.PeerColumnGather(m, n, torch.bfloat16, dev)
+        w, sc = sharded.shard_weight(d["weight_nk"], d["scale"], rank=rank, world=world)
+        for _ in range(2):                                # buffers are reused from step to step
+            _cabi.quant_matmul(q.to(dev), w.to(dev).t(), sc.to(dev), pertoken_scale=s.to(dev),
+                               output_dtype=torch.bfloat16, out=gat.local_block())
+            full = gat.gather()
+            torch.cuda.synchronize()
+            ok = torch.equal(full.cpu().view(torch.int16), want.view(torch.int16))
+            dist.barrier()
+        results.put((rank, "ok" if ok else "mismatch"))
+        dist.destroy_process_group()
+    except Exception as e:                                # pragma: no cover
+        results.put((rank, f"fail:{type(e).__name__}:{e}"))
+
+
+def test_two_rank_peer_gather_matches_unsharded_oracle():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = dict(results.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+    assert out == {0: "ok", 1: "ok"}, out
