@@ -165,24 +165,35 @@ def run_b200(args):
     def ev():
         return torch.cuda.Event(enable_timing=True)
 
-    comm = torch.cuda.Stream(device=device) if world > 1 else None
+    # high priority: the exchange kernel is small and must get its CTAs resident before the next GEMM fills the SMs
+    comm = torch.cuda.Stream(device=device, priority=-1) if world > 1 else None
 
     def gemm(q, w_t, scale, s, gat):
         if exchange == "p2p_scatter":      # C-ABI call with the output placed inside the peer-mapped matrix
             return _cabi.quant_matmul(q, w_t, scale, pertoken_scale=s, output_dtype=torch.bfloat16, out=gat.local_block())
         return ops.npu_quant_matmul(q, w_t, scale, pertoken_scale=s, output_dtype=torch.bfloat16)
 
-    def gather_async(gat, y):
+    comm_events = []
+
+    def gather_async(gat, y, record=False):
         """Exchange on the side stream so that it overlaps the next GEMM (independent data)."""
         if world == 1:
             return y
         main = torch.cuda.current_stream()
         comm.wait_stream(main)
         with torch.cuda.stream(comm):
+            if record:
+                a, b = ev(), ev()
+                a.record()
             if exchange == "p2p_scatter":
-                return gat.gather()
-            y.record_stream(comm)
-            return gat.gather(y)
+                out = gat.gather()
+            else:
+                y.record_stream(comm)
+                out = gat.gather(y)
+            if record:
+                b.record()
+                comm_events.append((a, b))
+            return out
 
     def step(x, x_down, record=False):
         e = [ev() for _ in range(6)] if record else None
@@ -191,13 +202,13 @@ def run_b200(args):
         if record: e[1].record()
         y1 = gemm(q, w_gu_t, d["s_gu"], s, gat_gu if world > 1 else None)
         if record: e[2].record()
-        o1 = gather_async(gat_gu, y1)
+        o1 = gather_async(gat_gu, y1, record)
         if record: e[3].record()
         q2, s2 = ops.npu_dynamic_quant(x_down, smooth_scales=d["smooth_down"])
         if record: e[4].record()
         y2 = gemm(q2, w_dn_t, d["s_dn"], s2, gat_dn if world > 1 else None)
         if record: e[5].record()
-        o2 = gather_async(gat_dn, y2)
+        o2 = gather_async(gat_dn, y2, record)
         if world > 1:
             torch.cuda.current_stream().wait_stream(comm)      # the step ends when both gathers have landed
         if record:
@@ -300,6 +311,8 @@ def run_b200(args):
         recv = (world - 1) / world * (M * 2 * FFN + M * HIDDEN) * 2
         out["gather_link_floor_ms"] = round(recv / 770e9 * 1e3, 4)
         out["exchange"] = exchange
+        out["exchange_ms_on_side_stream"] = {"gate_up": round(time_events(comm_events[0::2]) / max(1, len(comm_events[0::2])), 4),
+                                             "down": round(time_events(comm_events[1::2]) / max(1, len(comm_events[1::2])), 4)}
         out["gather_note"] = ("p2p_scatter: the GEMM writes its column block into a peer-mapped [M,N] matrix and "
                               "b200q_scatter_columns pushes it to every peer with 128-bit stores over NVLink, then a "
                               "device-side barrier; nccl_all_gather: all_gather_into_tensor plus one re-interleave copy. "

@@ -20,17 +20,36 @@ struct PeerList {
   int count;
 };
 
+// Each thread moves kUnroll 16-byte vectors per trip (loads first, then all remote stores), so that a
+// partly occupied SM - the kernel usually shares the GPU with the next GEMM - still keeps enough
+// stores in flight to fill the links.
+constexpr int kUnroll = 4;
+
 __global__ void __launch_bounds__(256) scatter_columns_kernel(const uint8_t* __restrict__ src, PeerList peers,
                                                              int64_t rows, int64_t row_stride, int64_t col_offset,
                                                              int64_t vecs_per_row) {
   const int64_t total = rows * vecs_per_row;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / vecs_per_row, v = i - r * vecs_per_row;
-    const int64_t off = r * row_stride + col_offset + v * 16;
-    const uint4 val = __ldcs(reinterpret_cast<const uint4*>(src + off));
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t base = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; base < total; base += step * kUnroll) {
+    uint4 val[kUnroll];
+    int64_t off[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t i = base + u * step;
+      off[u] = -1;
+      if (i < total) {
+        const int64_t r = i / vecs_per_row, v = i - r * vecs_per_row;
+        off[u] = r * row_stride + col_offset + v * 16;
+        val[u] = __ldcs(reinterpret_cast<const uint4*>(src + off[u]));
+      }
+    }
 #pragma unroll 1
-    for (int p = 0; p < peers.count; ++p)
-      *reinterpret_cast<uint4*>(static_cast<uint8_t*>(peers.dst[p]) + off) = val;
+    for (int p = 0; p < peers.count; ++p) {
+      uint8_t* dst = static_cast<uint8_t*>(peers.dst[p]);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (off[u] >= 0) *reinterpret_cast<uint4*>(dst + off[u]) = val[u];
+    }
   }
 }
 
@@ -59,7 +78,7 @@ extern "C" int b200q_scatter_columns(const void* src, void* const* peer_dst, int
     peers.dst[i] = peer_dst[i];
   }
   const int64_t vecs_per_row = block_bytes / 16;
-  const int64_t want = ceil_div(rows * vecs_per_row, 256);
+  const int64_t want = ceil_div(rows * vecs_per_row, 256 * kUnroll);
   const int64_t cap = (int64_t)sm_count() * 4;
   scatter_columns_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(src), peers, rows, row_stride_bytes, col_offset_bytes, vecs_per_row);
