@@ -147,11 +147,11 @@ struct X2<__half> {
 // The dequantisation repeats the reference golden's arithmetic in the activation dtype
 // (test/contrib/test_linear_weight_quant.py:21-26): w + offset rounded to 16 bits, then the product
 // with scale rounded again.  Integer weights are exact in fp16 and bf16.
-template <typename XT>
-__device__ __forceinline__ uint32_t add_mul2(uint32_t w2, uint32_t of2, uint32_t sc2, bool has_offset) {
+template <typename XT, bool HAS_OFF>
+__device__ __forceinline__ uint32_t add_mul2(uint32_t w2, uint32_t of2, uint32_t sc2) {
   using V = typename X2<XT>::type;
   V w = *reinterpret_cast<const V*>(&w2);
-  if (has_offset) w = __hadd2(w, *reinterpret_cast<const V*>(&of2));
+  if (HAS_OFF) w = __hadd2(w, *reinterpret_cast<const V*>(&of2));
   V r = __hmul2(w, *reinterpret_cast<const V*>(&sc2));
   return *reinterpret_cast<uint32_t*>(&r);
 }
@@ -229,90 +229,109 @@ struct WqCfg {
   static_assert(kDynamic <= 227 * 1024 && kDynamic > 116 * 1024, "shared memory budget; one CTA per SM");
 };
 
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts_u128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // Dequantises one packed [64 k x 256 n] tile into the UMMA B-operand tile with the GT threads of a
-// warp group (thread index lg).  Packed words are fetched in batches before any arithmetic so that
-// shared-memory latency and the dependent 16-bit operations of different items overlap.
-template <int LAYOUT, typename XT, int GT>
-__device__ __forceinline__ void dequant_tile(const uint8_t* __restrict__ raw, uint8_t* __restrict__ b_tile, int lg,
-                                             const uint32_t (&sc2)[4], const uint32_t (&of2)[4], bool has_off,
-                                             const WqParams& p, int64_t g, int64_t n_tile0) {
+// warp group (thread index lg).  raw and b_tile are shared-memory addresses.  Packed words are
+// fetched in batches before any arithmetic so that shared-memory latency and the dependent 16-bit
+// operations of different items overlap.  Every address is a per-thread constant plus a
+// compile-time offset.
+template <int LAYOUT, typename XT, int GT, bool HAS_OFF>
+__device__ __forceinline__ void dequant_tile(uint32_t raw, uint32_t b_tile, int lg, const uint32_t (&sc2)[4],
+                                             const uint32_t (&of2)[4], const WqParams& p, int64_t g, int64_t n_tile0) {
   constexpr int ITEMS = (kWqBK * (kWqTileN / 8)) / GT;      // 8-value items per thread (2048 per tile)
   constexpr int BATCH = ITEMS < 8 ? ITEMS : 8;
   if constexpr (LAYOUT != kW8K) {
-    const int wc = lg & 31;                                  // 8-channel group inside the tile
+    static_assert(GT == 256, "a thread's items are 8 k rows apart: one 1024-byte operand group per item");
+    constexpr uint32_t kWord = LAYOUT == kW4N ? 4 : 8;      // packed bytes per 8 channels
+    const uint32_t wc = lg & 31;                             // 8-channel group inside the tile
+    const uint32_t r = (lg >> 5) & 7;                        // k row inside every 8-row group
     const uint32_t ng = wc >> 3, c = wc & 7;                 // 64-channel block, 16-byte chunk in its 128-byte row
+    const uint32_t src = raw + (r * 32 + wc) * kWord;        // item i: k row r + 8 i
+    // MN-major operand: [64-channel block][8-k group][k row of 128 B][16-byte chunk ^ row]
+    const uint32_t dst = b_tile + ng * 8192 + r * 128 + ((c ^ r) << 4);
 #pragma unroll
     for (int b0 = 0; b0 < ITEMS; b0 += BATCH) {
       uint2 v[BATCH];
 #pragma unroll
       for (int i = 0; i < BATCH; ++i) {
-        const int kr = (lg >> 5) + (GT / 32) * (b0 + i);
-        if constexpr (LAYOUT == kW4N) v[i] = make_uint2(reinterpret_cast<const uint32_t*>(raw)[kr * 32 + wc], 0u);
-        else v[i] = reinterpret_cast<const uint2*>(raw)[kr * 32 + wc];
+        if constexpr (LAYOUT == kW4N) v[i] = make_uint2(lds_u32(src + (b0 + i) * 8 * 32 * kWord), 0u);
+        else v[i] = lds_u64(src + (b0 + i) * 8 * 32 * kWord);
       }
 #pragma unroll
       for (int i = 0; i < BATCH; ++i) {
-        const int kr = (lg >> 5) + (GT / 32) * (b0 + i);
         uint32_t o[4];
         if constexpr (LAYOUT == kW4N) {
           // halves of o[j]: values j and j+4 -> stored in the order (v0,v4,v1,v5,v2,v6,v3,v7)
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            o[j] = add_mul2<XT>(nibbles_to_x2<XT>(v[i].x >> (4 * j)), of2[j], sc2[j], has_off);
+          for (int j = 0; j < 4; ++j) {
+            o[j] = add_mul2<XT, HAS_OFF>(nibbles_to_x2<XT>(v[i].x >> (4 * j)), of2[j], sc2[j]);
+          }
         } else {
           const uint32_t w2[2] = {v[i].x, v[i].y};
 #pragma unroll
           for (int j = 0; j < 8; j += 2) {
             const float a = (float)(int8_t)(w2[j >> 2] >> (8 * (j & 3)));
             const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
-            o[j >> 1] = add_mul2<XT>(X2<XT>::pack(a, b), of2[j >> 1], sc2[j >> 1], has_off);
+            o[j >> 1] = add_mul2<XT, HAS_OFF>(X2<XT>::pack(a, b), of2[j >> 1], sc2[j >> 1]);
           }
         }
-        // MN-major operand: [64-channel block][8-k group][k row of 128 B][16-byte chunk ^ row]
-        const uint32_t r = kr & 7;
-        *reinterpret_cast<uint4*>(b_tile + ng * 8192 + (kr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
-            make_uint4(o[0], o[1], o[2], o[3]);
+        sts_u128(dst + (b0 + i) * 1024, o[0], o[1], o[2], o[3]);
       }
     }
   } else {
+    static_assert(GT == 256, "a thread's items are 32 channel rows apart: four 1024-byte operand groups per item");
     const uint32_t c = lg & 7;                               // 8-wide k chunk inside the 64-deep block
-    const uint2* raw64 = reinterpret_cast<const uint2*>(raw);
+    const uint32_t nr0 = (uint32_t)lg >> 3;                  // channel row of item 0; item i: nr0 + 32 i
+    const uint32_t r = nr0 & 7;
+    const uint32_t src = raw + (nr0 * 8 + c) * 8;
+    // K-major operand: [8-channel group][channel row of 128 B][16-byte chunk ^ row]
+    const uint32_t dst = b_tile + (nr0 >> 3) * 1024 + r * 128 + ((c ^ r) << 4);
+    const XT* sc_row = static_cast<const XT*>(p.scale) + g * p.n + n_tile0 + nr0;
+    const XT* of_row = HAS_OFF ? static_cast<const XT*>(p.offset) + g * p.n + n_tile0 + nr0 : nullptr;
+    const int64_t n_left = p.n - n_tile0 - nr0;              // channels from this thread's first row to the end
 #pragma unroll
     for (int b0 = 0; b0 < ITEMS; b0 += BATCH) {
       uint2 v[BATCH];
       uint32_t s2[BATCH], o2[BATCH];
 #pragma unroll
       for (int i = 0; i < BATCH; ++i) {
-        const int nr = (lg >> 3) + (GT / 8) * (b0 + i);      // channel row inside the tile
-        const int64_t n = n_tile0 + nr;
-        const bool nv = n < p.n;
-        const float scv = nv ? X2<XT>::to_float(static_cast<const XT*>(p.scale)[g * p.n + n]) : 0.0f;
-        const float ofv = (nv && has_off) ? X2<XT>::to_float(static_cast<const XT*>(p.offset)[g * p.n + n]) : 0.0f;
+        const bool nv = 32 * (b0 + i) < n_left;
+        const float scv = nv ? X2<XT>::to_float(sc_row[32 * (b0 + i)]) : 0.0f;
+        const float ofv = (nv && HAS_OFF) ? X2<XT>::to_float(of_row[32 * (b0 + i)]) : 0.0f;
         s2[i] = X2<XT>::pack(scv, scv);
         o2[i] = X2<XT>::pack(ofv, ofv);
-        v[i] = raw64[nr * 8 + c];
+        v[i] = lds_u64(src + (b0 + i) * 32 * 8 * 8);
       }
 #pragma unroll
       for (int i = 0; i < BATCH; ++i) {
-        const int nr = (lg >> 3) + (GT / 8) * (b0 + i);
         const uint32_t w2[2] = {v[i].x, v[i].y};
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 8; j += 2) {
           const float a = (float)(int8_t)(w2[j >> 2] >> (8 * (j & 3)));
           const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
-          o[j >> 1] = add_mul2<XT>(X2<XT>::pack(a, b), o2[i], s2[i], has_off);
+          o[j >> 1] = add_mul2<XT, HAS_OFF>(X2<XT>::pack(a, b), o2[i], s2[i]);
         }
-        // K-major operand: [8-channel group][channel row of 128 B][16-byte chunk ^ row]
-        const uint32_t r = nr & 7;
-        *reinterpret_cast<uint4*>(b_tile + (nr >> 3) * 1024 + r * 128 + ((c ^ r) << 4)) =
-            make_uint4(o[0], o[1], o[2], o[3]);
+        sts_u128(dst + (b0 + i) * 4 * 1024, o[0], o[1], o[2], o[3]);
       }
     }
   }
 }
 
-template <int LAYOUT, typename XT, int MM, int NCH>
+template <int LAYOUT, typename XT, int MM, int NCH, bool HAS_OFF>
 __global__ void __launch_bounds__(kWqThreads, 1)
 wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const WqParams p) {
   using C = WqCfg<LAYOUT, MM, NCH>;
@@ -365,6 +384,11 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       WQ_DIAG_BEGIN();
       WqWalk walk(p, blockIdx.x, gridDim.x);
       int unit, kb0, kb1;
+      auto weight_coords = [&](int tn, int kb, int& c0, int& c1) {
+        if (LAYOUT == kW4N) { c0 = tn * 128; c1 = kb * kWqBK; }            // bytes of packed nibbles: 128 bytes = 256 channels per row of k
+        else if (LAYOUT == kW8N) { c0 = tn * kWqTileN; c1 = kb * kWqBK; }
+        else { c0 = kb * kWqBK; c1 = tn * kWqTileN; }                      // k-contiguous: rows are channels
+      };
       while (ok && walk.next(unit, kb0, kb1)) {
         const int tn = unit % p.tiles_n, mc = unit / p.tiles_n;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -373,13 +397,9 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           if (!mbar_wait(&done[stage], (uint32_t)((it / LS) & 1) ^ 1u, abort_flag, kDevTimeoutProducer)) { ok = false; break; }
           WQ_DIAG_ADD(d_wait);
           mbar_arrive_expect_tx(&full[stage], C::kRawBytes + C::kXBytes);
-          uint8_t* raw = sRaw + stage * C::kRawBytes;
-          if (LAYOUT == kW4N)        // bytes of packed nibbles: 128 bytes = 256 channels per row of k
-            tma_load_2d(raw, &tmW, &full[stage], tn * 128, kb * kWqBK);
-          else if (LAYOUT == kW8N)
-            tma_load_2d(raw, &tmW, &full[stage], tn * kWqTileN, kb * kWqBK);
-          else                       // k-contiguous: rows are channels
-            tma_load_2d(raw, &tmW, &full[stage], kb * kWqBK, tn * kWqTileN);
+          int c0, c1;
+          weight_coords(tn, kb, c0, c1);
+          tma_load_2d(sRaw + stage * C::kRawBytes, &tmW, &full[stage], c0, c1);
 #pragma unroll
           for (int ch = 0; ch < NCH; ++ch)
             tma_load_2d(sX + stage * C::kXBytes + ch * MM * 128, &tmX, &full[stage], kb * kWqBK, (mc * NCH + ch) * MM);
@@ -450,7 +470,9 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int group = dw / (kWqDeqWarps / kWqGroups);
     const int lg = (dw % (kWqDeqWarps / kWqGroups)) * 32 + lane;   // thread index inside the group
     const int quad = warp & 3;                         // TMEM lane quadrant of this warp
-    const bool has_off = p.offset != nullptr;
+    // Quantisation groups are whole K blocks (checked on the host); 0 = one group per channel.
+    const uint32_t gs_blocks = p.group_size > 0 ? (uint32_t)(p.group_size / kWqBK) : 0u;
+    const uint32_t sRaw_u32 = smem_u32(sRaw), sB_u32 = smem_u32(sB);
     int it_base = 0;                                   // K blocks this CTA has been through before this segment
     uint32_t tphase = 0;
     bool ok = true;
@@ -466,25 +488,23 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       uint32_t sc2[4], of2[4];   // this thread's 8 channels as 16-bit pairs: kW4N (j, j+4), kW8N (2j, 2j+1)
       uint4 ns, no;              // parameters fetched ahead for the next K block of this group
       const int64_t n_oct0 = n_tile0 + (lg & 31) * 8;
-      auto quant_group = [&](int kb) -> int64_t { return p.group_size > 0 ? ((int64_t)kb * kWqBK) / p.group_size : 0; };
       int kb = kb0 + ((group - it_base % kWqGroups + kWqGroups) % kWqGroups);   // first K block owned by the group
-      int64_t g_next = quant_group(kb);
+      // Group of the K block ahead, kept by counting (no division in the loop).
+      uint32_t g_next = gs_blocks ? (uint32_t)kb / gs_blocks : 0u;
+      uint32_t g_rem = gs_blocks ? (uint32_t)kb % gs_blocks : 0u;
       if (LAYOUT != kW8K && kb < kb1) fetch_params8<XT>(p, g_next, n_oct0, ns, no);
       for (; kb < kb1; kb += kWqGroups) {
         const int it = it_base + (kb - kb0);
         const int stage = it % LS, slot = it % AS;
         const int64_t g = g_next;
-        if (LAYOUT != kW8K) {
-          if (g != cur_group) {
-            cur_group = g;
-            pair_params8<LAYOUT>(ns, no, sc2, of2);
-          }
-          if (kb + kWqGroups < kb1) {                  // loads for the group's next K block fly during this one
-            g_next = quant_group(kb + kWqGroups);
-            if (g_next != g) fetch_params8<XT>(p, g_next, n_oct0, ns, no);
-          }
-        } else if (kb + kWqGroups < kb1) {
-          g_next = quant_group(kb + kWqGroups);
+        if (LAYOUT != kW8K && g != cur_group) {
+          cur_group = g;
+          pair_params8<LAYOUT>(ns, no, sc2, of2);
+        }
+        if (gs_blocks && kb + kWqGroups < kb1) {       // loads for the group's next K block fly during this one
+          g_rem += kWqGroups;
+          while (g_rem >= gs_blocks) { g_rem -= gs_blocks; ++g_next; }
+          if (LAYOUT != kW8K && (int64_t)g_next != g) fetch_params8<XT>(p, g_next, n_oct0, ns, no);
         }
         WQ_DIAG_ADD(d_work);
         // The tile must have landed, and the MMAs that read this operand slot AS tiles ago must have retired.
@@ -493,8 +513,8 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           got = mbar_wait(&done[(it - AS) % LS], (uint32_t)((it - AS) / LS) & 1u, abort_flag, kDevTimeoutEpilogue);
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }   // warp-uniform, the warp stays converged
         WQ_DIAG_ADD(d_wait);
-        dequant_tile<LAYOUT, XT, GT>(sRaw + stage * C::kRawBytes, sB + slot * kWqBBytes, lg, sc2, of2, has_off, p, g,
-                                     n_tile0);
+        dequant_tile<LAYOUT, XT, GT, HAS_OFF>(sRaw_u32 + stage * C::kRawBytes, sB_u32 + slot * kWqBBytes, lg, sc2, of2,
+                                              p, g, n_tile0);
         fence_proxy_async_smem();                      // generic-proxy stores -> visible to the MMA (async proxy)
         __syncwarp();
         if (lane == 0) mbar_arrive(&aready[slot]);
@@ -609,20 +629,46 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 }
 
 // stream-K: adds the fp32 partial tiles of every unit that was shared by several CTAs, in CTA
-// order, then bias and cast.  Units computed whole by one CTA were written by that CTA.
+// order, then bias and cast.  Units computed whole by one CTA were written by that CTA.  One CTA
+// (256 threads = 4 rows x 64 four-channel vectors) per 16-row slice of a unit.
 template <typename XT>
-__global__ void wq_finalize_kernel(const WqParams p, int mm_rows) {
-  const int64_t total = p.m * p.n;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t token = i / p.n, n = i - token * p.n;
-    const int64_t unit = (token / mm_rows) * p.tiles_n + n / kWqTileN;
-    const int first = wq_cta_of_item(unit * p.kblocks, p.total_items, p.ctas);
-    const int last = wq_cta_of_item((unit + 1) * p.kblocks - 1, p.total_items, p.ctas);
-    if (last == first) continue;
-    float v = 0.0f;
-    for (int c = 0; c <= last - first; ++c) v = __fadd_rn(v, p.parts[((int64_t)c * p.m + token) * p.n + n]);
-    if (p.bias) v = __fadd_rn(v, X2<XT>::to_float(static_cast<const XT*>(p.bias)[n]));
-    static_cast<XT*>(p.out)[i] = X2<XT>::from_float(v);
+__global__ void __launch_bounds__(256) wq_finalize_kernel(const WqParams p, int mm_rows) {
+  __shared__ int s_first, s_last;
+  const int slices = mm_rows / 16;
+  const int c4 = threadIdx.x & 63, rsub = threadIdx.x >> 6;
+  for (int64_t w = blockIdx.x; w < (int64_t)p.units * slices; w += gridDim.x) {
+    const int unit = (int)(w / slices), sl = (int)(w - (int64_t)unit * slices);
+    const int tn = unit % p.tiles_n, mc = unit / p.tiles_n;
+    const int64_t row0 = (int64_t)mc * mm_rows + sl * 16;
+    if (row0 >= p.m) continue;                               // block-uniform
+    __syncthreads();                                         // the previous slice's readers are done
+    if (threadIdx.x == 0) {
+      s_first = wq_cta_of_item((int64_t)unit * p.kblocks, p.total_items, p.ctas);
+      s_last = wq_cta_of_item((int64_t)(unit + 1) * p.kblocks - 1, p.total_items, p.ctas);
+    }
+    __syncthreads();
+    const int parts = s_last - s_first + 1;
+    if (parts <= 1) continue;
+    const int64_t n = (int64_t)tn * kWqTileN + c4 * 4;
+    if (n >= p.n) continue;
+    float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (p.bias) {
+      const XT* bp = static_cast<const XT*>(p.bias) + n;
+      b = make_float4(X2<XT>::to_float(bp[0]), X2<XT>::to_float(bp[1]), X2<XT>::to_float(bp[2]), X2<XT>::to_float(bp[3]));
+    }
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) {
+      const int64_t token = row0 + rr * 4 + rsub;
+      if (token >= p.m) break;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int c = 0; c < parts; ++c) {
+        const float4 t = __ldcs(reinterpret_cast<const float4*>(p.parts + ((int64_t)c * p.m + token) * p.n + n));
+        v.x = __fadd_rn(v.x, t.x); v.y = __fadd_rn(v.y, t.y); v.z = __fadd_rn(v.z, t.z); v.w = __fadd_rn(v.w, t.w);
+      }
+      if (p.bias) { v.x = __fadd_rn(v.x, b.x); v.y = __fadd_rn(v.y, b.y); v.z = __fadd_rn(v.z, b.z); v.w = __fadd_rn(v.w, b.w); }
+      *reinterpret_cast<uint2*>(static_cast<XT*>(p.out) + token * p.n + n) =
+          make_uint2(X2<XT>::pack(v.x, v.y), X2<XT>::pack(v.z, v.w));
+    }
   }
 }
 
@@ -673,9 +719,12 @@ WqPlan wq_plan(int64_t m, int64_t k, int64_t n) {
   pl.units = (int)units;
   pl.total_items = units * pl.kblocks;
   const int sms = sm_count();
-  // Splitting K costs an fp32 partial tile per (CTA, tile) pair: worth it for very few tokens (measured: up to ~16), where the
-  // partials are small next to the weight stream, or when whole tiles would leave most SMs idle.
-  pl.stream_k = (pl.kblocks >= 2 && ((m <= 16 && units < 4LL * sms) || 2 * units < sms)) ? 1 : 0;
+  // Splitting K costs an fp32 partial tile per (CTA, tile) pair.  It pays when whole tiles would leave
+  // SMs idle in the last round (less than 90 % of the SM-rounds used) and the partials stay small next
+  // to the weight stream, or when most SMs would have no tile at all.
+  const int64_t rounds = ceil_div(units, (int64_t)sms);
+  const bool uneven = units * 10 < rounds * sms * 9;
+  pl.stream_k = (pl.kblocks >= 2 && ((uneven && 128 * m <= k && units < 4LL * sms) || 2 * units < sms)) ? 1 : 0;
   if (const char* env = getenv("B200Q_WQ_STREAMK")) pl.stream_k = (env[0] != '0' && pl.kblocks >= 2) ? 1 : 0;   // tuning override
   pl.ctas = (int)(pl.stream_k ? (pl.total_items < sms ? pl.total_items : sms) : (units < sms ? units : sms));
   pl.max_parts = 0;
@@ -690,10 +739,10 @@ WqPlan wq_plan(int64_t m, int64_t k, int64_t n) {
   return pl;
 }
 
-template <int LAYOUT, typename XT, int MM, int NCH>
+template <int LAYOUT, typename XT, int MM, int NCH, bool HAS_OFF>
 int launch_wq(const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p, cudaStream_t st) {
   using C = WqCfg<LAYOUT, MM, NCH>;
-  auto kern = wq_umma_kernel<LAYOUT, XT, MM, NCH>;
+  auto kern = wq_umma_kernel<LAYOUT, XT, MM, NCH, HAS_OFF>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -706,8 +755,7 @@ int launch_wq(const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p,
   kern<<<p.ctas, kWqThreads, C::kDynamic, st>>>(tmW, tmX, p);
   if (int rc = check_launch("weight_quant_matmul (tcgen05)")) return rc;
   if (p.parts) {
-    const int64_t total = p.m * p.n;
-    const int64_t want = ceil_div(total, 256);
+    const int64_t want = (int64_t)p.units * (MM * NCH / 16);
     const int blocks = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
     wq_finalize_kernel<XT><<<blocks, 256, 0, st>>>(p, MM * NCH);
     return check_launch("weight_quant_matmul (stream-K sum)");
@@ -715,20 +763,24 @@ int launch_wq(const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p,
   return B200Q_OK;
 }
 
-template <int LAYOUT, typename XT>
+template <int LAYOUT, typename XT, bool HAS_OFF>
 int dispatch_mm(int mm, const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p, cudaStream_t st) {
-  if (mm == 64) return launch_wq<LAYOUT, XT, 64, 1>(tmW, tmX, p, st);
-  if (mm == 128) return launch_wq<LAYOUT, XT, 128, 1>(tmW, tmX, p, st);
-  return launch_wq<LAYOUT, XT, 128, 2>(tmW, tmX, p, st);     // mm == 256: two 128-token chunks per weight tile
+  if (mm == 64) return launch_wq<LAYOUT, XT, 64, 1, HAS_OFF>(tmW, tmX, p, st);
+  if (mm == 128) return launch_wq<LAYOUT, XT, 128, 1, HAS_OFF>(tmW, tmX, p, st);
+  return launch_wq<LAYOUT, XT, 128, 2, HAS_OFF>(tmW, tmX, p, st);   // mm == 256: two 128-token chunks per weight tile
+}
+template <int LAYOUT, typename XT>
+int dispatch_off(int mm, const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p, cudaStream_t st) {
+  return p.offset ? dispatch_mm<LAYOUT, XT, true>(mm, tmW, tmX, p, st) : dispatch_mm<LAYOUT, XT, false>(mm, tmW, tmX, p, st);
 }
 
 template <typename XT>
 int dispatch_layout(int layout, int mm, const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p,
                     cudaStream_t st) {
   switch (layout) {
-    case kW4N: return dispatch_mm<kW4N, XT>(mm, tmW, tmX, p, st);
-    case kW8N: return dispatch_mm<kW8N, XT>(mm, tmW, tmX, p, st);
-    default: return dispatch_mm<kW8K, XT>(mm, tmW, tmX, p, st);
+    case kW4N: return dispatch_off<kW4N, XT>(mm, tmW, tmX, p, st);
+    case kW8N: return dispatch_off<kW8N, XT>(mm, tmW, tmX, p, st);
+    default: return dispatch_off<kW8K, XT>(mm, tmW, tmX, p, st);
   }
 }
 
