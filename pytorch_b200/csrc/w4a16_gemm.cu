@@ -55,7 +55,9 @@ constexpr int kWqDeqWarps = 16;
 constexpr int kWqGroups = 2;                // groups of dequantising warps
 constexpr int kWqGroupThreads = kWqDeqWarps / kWqGroups * 32;
 constexpr int kWqDeqThreads = kWqDeqWarps * 32;
-constexpr int kWqThreads = 64 + kWqDeqThreads;
+constexpr int kWqProducers = 1;                   // warps issuing TMA loads, one lane each
+constexpr int kWqMmaWarp = kWqProducers;
+constexpr int kWqThreads = (kWqProducers + 1) * 32 + kWqDeqThreads;
 constexpr int kWqBBytes = kWqTileN * kWqBK * 2;   // one dequantised operand tile
 
 enum WqLayout { kW4N = 0, kW8N = 1, kW8K = 2 };   // int4 [k,n/8]; int8 n-contiguous; int8 k-contiguous
@@ -226,6 +228,9 @@ struct WqCfg {
   static constexpr int kDynamic = kTotal + 1024;
   static constexpr uint32_t kTmemCols = NCH * kWqTileN;
   static_assert(kLoadStages > kASlots && kLoadStages > kWqGroups, "ring depths");
+  // A producer moves from K block it to it + kWqProducers; the stage of the second one must have been
+  // used last by a K block no later than it, or its wait could pass a whole phase early.
+  static_assert(kLoadStages >= kWqProducers, "more producers than load stages");
   static_assert(kDynamic <= 227 * 1024 && kDynamic > 116 * 1024, "shared memory budget; one CTA per SM");
 };
 
@@ -365,7 +370,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     prefetch_tensormap(&tmW);
     prefetch_tensormap(&tmX);
   }
-  if (warp == 1) {
+  if (warp == kWqMmaWarp) {
     tmem_alloc(tmem_holder, C::kTmemCols);
     tmem_relinquish();
   }
@@ -374,8 +379,11 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+  if (warp < kWqProducers) {
+    // ----------------------------------------------------------- TMA producers
+    // K block `it` of this CTA's sequence is loaded by producer it % kWqProducers.  (Loads issued by one
+    // thread are served a few at a time, so a pure copy streams faster from several issuing warps; this
+    // kernel is bound by shared-memory bandwidth and the tensor pipe instead and runs best with one.)
     if (lane == 0) {
       int it = 0;
       bool ok = true;
@@ -392,6 +400,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       while (ok && walk.next(unit, kb0, kb1)) {
         const int tn = unit % p.tiles_n, mc = unit / p.tiles_n;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          if (it % kWqProducers != warp) continue;
           const int stage = it % LS;
           WQ_DIAG_ADD(d_issue);
           if (!mbar_wait(&done[stage], (uint32_t)((it / LS) & 1) ^ 1u, abort_flag, kDevTimeoutProducer)) { ok = false; break; }
@@ -410,7 +419,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       if (!ok)
         for (int i = 0; i < 200; ++i) __nanosleep(1000);   // let copies in flight land before smem is released
     }
-  } else if (warp == 1) {
+  } else if (warp == kWqMmaWarp) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t fmt = std::is_same<XT, __nv_bfloat16>::value ? 1u : 0u;
@@ -466,7 +475,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   } else {
     // ------------------------------------------- dequantise, then epilogue
     constexpr int GT = kWqGroupThreads;
-    const int dw = warp - 2;                           // 0..15
+    const int dw = warp - (kWqProducers + 1);          // 0..15
     const int group = dw / (kWqDeqWarps / kWqGroups);
     const int lg = (dw % (kWqDeqWarps / kWqGroups)) * 32 + lane;   // thread index inside the group
     const int quad = warp & 3;                         // TMEM lane quadrant of this warp
@@ -612,7 +621,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       if (lane == 0) mbar_arrive(tempty);
       WQ_DIAG_ADD(d_epi);
     }
-    if (threadIdx.x == 64) {
+    if (dw == 0 && lane == 0) {
       WQ_DIAG_STORE(6, d_wait);
       WQ_DIAG_STORE(7, d_work);
       WQ_DIAG_STORE(8, d_epi);
@@ -621,7 +630,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kWqMmaWarp) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
