@@ -59,6 +59,20 @@ int b200q_device_error(unsigned int* code, int reset);
 int b200q_dynamic_quant(const void* x, int x_dtype, const void* smooth, int smooth_dtype, int8_t* y,
                         float* scale, int64_t rows, int64_t k, void* stream);
 
+/* npu_dynamic_quant(input, smooth_scales, group_index) and
+ * npu_dynamic_quant_asymmetric(input, smooth_scales, group_index) -> (int8 y, f32 scale, f32 offset)
+ *   replace op_plugin::npu_dynamic_quant / npu_dynamic_quant_asymmetric (aclnnDynamicQuantV2), reached from
+ *   torch_npu/onnx/wrapper_onnx_ops.py:743-745 and :762-767; output contracts test/test_fake_tensor.py:1671-1709,
+ *   group_index usage test/onnx/test_wrapper_onnx_ops.py:1335-1392.
+ * group_index (or NULL): int32 [n_groups], sorted cumulative end rows; row r uses smooth row g, the first g
+ * with r < group_index[g] (rows past the last entry use the last row); smooth is then [n_groups, k].
+ * offset == NULL: symmetric, as b200q_dynamic_quant.  offset != NULL: asymmetric, per row
+ * scale = (max(xs) - min(xs)) / 255, offset = 127 - max(xs) / scale,
+ * y = clamp(rint(xs / scale + offset), -128, 127); a constant row gives scale 0, offset 0, y 0. */
+int b200q_dynamic_quant_ext(const void* x, int x_dtype, const void* smooth, int smooth_dtype,
+                            const int32_t* group_index, int64_t n_groups, int8_t* y, float* scale, float* offset,
+                            int64_t rows, int64_t k, void* stream);
+
 /* npu_quant_matmul(x1, x2, scale, *, offset, pertoken_scale, bias, output_dtype)
  *   replaces op_plugin::npu_quant_matmul / aclnnQuantMatmulV3-V4, reached from
  *   torch_npu/contrib/module/linear_quant.py:110-112 and linear_a8w8_quant.py:117-120.
@@ -142,6 +156,15 @@ int b200q_weight_quant_matmul(const b200q_weight_quant_matmul_args* args, void* 
  *   The operator does not occur in the reference tree; the nibble order is the one its
  *   unpack helper expects, test/custom_ops/test_npu_anti_quant.py:12-24. */
 int b200q_int4pack(const int32_t* w, int32_t* packed, int64_t rows, int64_t cols, void* stream);
+
+/* npu_anti_quant(x, scale, *, offset=None, dst_dtype=None, src_dtype=None)
+ *   replaces op_plugin::npu_anti_quant / aclnnAscendAntiQuant (wrapper torch_npu/onnx/wrapper_onnx_ops.py:824-828;
+ *   golden test/custom_ops/test_npu_anti_quant.py:29-42, contract test/test_fake_tensor.py:1949-1959).
+ * x: int8 [rows, n] (src_bits 8) or int32 words of eight int4 values [rows, n/8] (src_bits 4, value j of a
+ * word in bits [4j, 4j+4)); scale, offset: [n] f32 or bf16 (offset may be NULL); out [rows, n] f16 or bf16.
+ * out = cast((float(x) + offset) * scale): fp32 sum, fp32 product, one rounding to the output type. */
+int b200q_anti_quant(const void* x, int src_bits, const void* scale, const void* offset, int param_dtype,
+                     void* out, int out_dtype, int64_t rows, int64_t n, void* stream);
 
 /* Exchange step of the column-sharded linear: pushes bytes [col_offset, col_offset + block_bytes) of
  * every row of the local [rows, row_stride_bytes] matrix `src` to the same place in each of the

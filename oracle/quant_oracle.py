@@ -23,8 +23,9 @@ from the CPU golden compositions the reference keeps in its own tests:
   ``test/custom_ops/test_npu_anti_quant.py:12-24``.
 
 PARITY STATUS: the reference holds no known-answer vectors for
-``npu_dynamic_quant``, ``npu_quant_matmul``, ``npu_convert_weight_to_int4pack``
-or group-wise W4A16 -> for those ops parity is UNPINNED.  Pinned pieces: the
+``npu_dynamic_quant`` (symmetric or asymmetric), ``npu_quant_matmul``,
+``npu_convert_weight_to_int4pack`` or group-wise W4A16 -> for those ops parity is
+UNPINNED.  ``npu_anti_quant`` is pinned by the reference's own golden function.  Pinned pieces: the
 int4 unpack convention, the ``(w+offset)*scale`` weight-only golden and the
 ``x1_scale*x2_scale*(x1@x2)`` dequant golden, all three checked against the
 reference's own helper functions through ``tests/golden/reference_goldens.npz``.
@@ -54,8 +55,23 @@ def _cast_out(a: np.ndarray, dtype: torch.dtype) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------- A1
-def dynamic_quant(x, smooth_scales=None):
-    """``npu_dynamic_quant(input, smooth_scales=None)`` -> (int8 y, fp32 scale).
+def _smoothed(x, smooth_scales, group_index):
+    """fp32 ``x * smooth``; with ``group_index`` (sorted cumulative end rows, one smooth row per
+    group; rows past the last entry use the last row: ``test/onnx/test_wrapper_onnx_ops.py:1345-1354``)."""
+    xs = _to_f32(x)
+    if smooth_scales is None:
+        return xs
+    sm = _to_f32(smooth_scales)
+    if group_index is None:
+        return xs * sm                               # fp32 multiply, one rounding
+    gi = np.asarray(group_index.detach().cpu().numpy() if isinstance(group_index, torch.Tensor) else group_index)
+    flat = xs.reshape(-1, xs.shape[-1])
+    g = np.minimum(np.searchsorted(gi, np.arange(flat.shape[0]), side="right"), len(gi) - 1)
+    return (flat * sm[g]).reshape(xs.shape)
+
+
+def dynamic_quant(x, smooth_scales=None, group_index=None):
+    """``npu_dynamic_quant(input, smooth_scales=None, group_index=None)`` -> (int8 y, fp32 scale).
 
     Per row of the last dimension: ``xs = x * smooth`` (fp32), ``amax = max|xs|``,
     ``scale = amax / 127`` (true division), ``y = clip(rint(xs / scale), -128, 127)``.
@@ -63,9 +79,7 @@ def dynamic_quant(x, smooth_scales=None):
     (int8 of the input's shape, fp32 of ``shape[:-1]``):
     ``test/test_fake_tensor.py:1671-1686``; formula: see the module docstring.
     """
-    xs = _to_f32(x)
-    if smooth_scales is not None:
-        xs = xs * _to_f32(smooth_scales)            # fp32 multiply, one rounding
+    xs = _smoothed(x, smooth_scales, group_index)
     amax = np.max(np.abs(xs), axis=-1) if xs.shape[-1] else np.zeros(xs.shape[:-1], F32)
     scale = (amax / F32(127.0)).astype(F32)
     safe = np.where(scale == 0, F32(1.0), scale)[..., None]
@@ -74,6 +88,40 @@ def dynamic_quant(x, smooth_scales=None):
     q = np.where(scale[..., None] == 0, F32(0.0), q)
     y = np.clip(q, -128, 127).astype(np.int8)
     return torch.from_numpy(y), torch.from_numpy(scale.astype(F32))
+
+
+def dynamic_quant_asymmetric(x, smooth_scales=None, group_index=None):
+    """``npu_dynamic_quant_asymmetric`` -> (int8 y, fp32 scale, fp32 offset); contract
+    ``test/test_fake_tensor.py:1690-1709``.  PARITY UNPINNED: the reference tree holds the output
+    contract only; the formula is the published one of the aclnn dynamic-quant operator it calls:
+    per row ``scale = (max(xs) - min(xs)) / 255``, ``offset = 127 - max(xs) / scale``,
+    ``y = clip(rint(xs / scale + offset), -128, 127)``, each step one fp32 rounding.  A constant
+    row gives ``scale = 0``, ``offset = 0``, ``y = 0`` (this build's choice)."""
+    xs = _smoothed(x, smooth_scales, group_index)
+    mx = np.max(xs, axis=-1).astype(F32)
+    mn = np.min(xs, axis=-1).astype(F32)
+    scale = ((mx - mn).astype(F32) / F32(255.0)).astype(F32)
+    zero = scale == 0
+    safe = np.where(zero, F32(1.0), scale)
+    offset = np.where(zero, F32(0.0), (F32(127.0) - (mx / safe).astype(F32)).astype(F32)).astype(F32)
+    with np.errstate(invalid="ignore", over="ignore"):
+        q = np.rint(((xs / safe[..., None]).astype(F32) + offset[..., None]).astype(F32))
+    q = np.where(zero[..., None], F32(0.0), q)
+    y = np.clip(q, -128, 127).astype(np.int8)
+    return torch.from_numpy(y), torch.from_numpy(scale), torch.from_numpy(offset)
+
+
+def anti_quant(x, scale, offset=None, dst_dtype=torch.float16, src_dtype=None):
+    """``npu_anti_quant(x, scale, offset=None, dst_dtype, src_dtype)``: int8, or int32 words of eight
+    int4 values, to fp16/bf16: ``cast((float(x) + offset) * scale)`` with an fp32 sum and an fp32
+    product (``test/custom_ops/test_npu_anti_quant.py:29-42``)."""
+    if x.dtype == torch.int32:
+        x = unpack_int4(x)
+    xf = x.detach().cpu().numpy().astype(F32)
+    sc = np.broadcast_to(_to_f32(scale), xf.shape)
+    if offset is not None:
+        xf = (xf + np.broadcast_to(_to_f32(offset), xf.shape)).astype(F32)
+    return _cast_out((xf * sc).astype(F32), dst_dtype)
 
 
 # --------------------------------------------------------------------------- A2

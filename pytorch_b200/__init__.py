@@ -6,7 +6,7 @@ the reference does in ``torch_npu/_init/core/_exports.py:45-51``, re-exports eve
 as an attribute of this package: ``pytorch_b200.npu_quant_matmul is torch.ops.npu.npu_quant_matmul``.
 
 There is no CPU, Triton or eager fallback.  If the extension has not been built the import
-raises; build it with ``python -m pytorch_b200._build``.
+raises; build it with ``python pytorch_b200/_build.py``.
 """
 from __future__ import annotations
 
@@ -23,13 +23,15 @@ OPS = (
     "npu_weight_quant_batchmatmul",
     "npu_convert_weight_to_int4pack",
     "npu_trans_quant_param",
+    "npu_dynamic_quant_asymmetric",
+    "npu_anti_quant",
 )
 
 
 def _load() -> None:
     if not _os.path.exists(_TORCH_LIB):
         raise ImportError(
-            f"{_TORCH_LIB} is missing: build the extension with `python -m pytorch_b200._build`; "
+            f"{_TORCH_LIB} is missing: build the extension with `python pytorch_b200/_build.py`; "
             "the operators have no fallback implementation")
     _torch.ops.load_library(_TORCH_LIB)
 
@@ -41,6 +43,8 @@ npu_quant_matmul = _torch.ops.npu.npu_quant_matmul
 npu_weight_quant_batchmatmul = _torch.ops.npu.npu_weight_quant_batchmatmul
 npu_convert_weight_to_int4pack = _torch.ops.npu.npu_convert_weight_to_int4pack
 npu_trans_quant_param = _torch.ops.npu.npu_trans_quant_param
+npu_dynamic_quant_asymmetric = _torch.ops.npu.npu_dynamic_quant_asymmetric
+npu_anti_quant = _torch.ops.npu.npu_anti_quant
 
 from . import contrib  # noqa: E402,F401
 

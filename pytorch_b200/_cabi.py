@@ -25,7 +25,7 @@ EXPORTS = (
     "b200q_dynamic_quant", "b200q_quant_matmul_workspace_bytes", "b200q_quant_matmul",
     "b200q_static_scratch_bytes", "b200q_quant_matmul_static_scratch",
     "b200q_weight_quant_matmul_workspace_bytes", "b200q_weight_quant_matmul", "b200q_int4pack",
-    "b200q_trans_quant_param", "b200q_scatter_columns",
+    "b200q_trans_quant_param", "b200q_scatter_columns", "b200q_dynamic_quant_ext", "b200q_anti_quant",
 )
 
 
@@ -73,7 +73,7 @@ def lib() -> C.CDLL:
     if _lib is None:
         path = os.environ.get("B200Q_LIB", _LIB_PATH)      # override: a differently built libb200q.so
         if not os.path.exists(path):
-            raise ImportError(f"{path} is missing: run `python -m pytorch_b200._build` "
+            raise ImportError(f"{path} is missing: run `python pytorch_b200/_build.py` "
                               "(there is no fallback implementation)")
         l = C.CDLL(path)
         l.b200q_version.restype = C.c_int
@@ -93,6 +93,10 @@ def lib() -> C.CDLL:
         l.b200q_weight_quant_matmul.argtypes = [C.POINTER(WeightQuantMatmulArgs), C.c_void_p]
         l.b200q_int4pack.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
         l.b200q_trans_quant_param.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p]
+        l.b200q_dynamic_quant_ext.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int64,
+                                              C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+        l.b200q_anti_quant.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
+                                       C.c_int64, C.c_int64, C.c_void_p]
         l.b200q_scatter_columns.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int64, C.c_int64, C.c_int64,
                                             C.c_int64, C.c_void_p]
         _lib = l
@@ -136,6 +140,41 @@ def dynamic_quant(x: torch.Tensor, smooth_scales: torch.Tensor | None = None):
     check(lib().b200q_dynamic_quant(_ptr(x), DTYPE[x.dtype], _ptr(sm), NONE if sm is None else DTYPE[sm.dtype],
                                     _ptr(y), _ptr(scale), rows, k, _stream()))
     return y, scale
+
+
+def dynamic_quant_ext(x: torch.Tensor, smooth_scales: torch.Tensor | None = None,
+                      group_index: torch.Tensor | None = None, asymmetric: bool = False):
+    """``b200q_dynamic_quant_ext``: per-group smooth scales and/or the asymmetric variant.
+    Returns (y, scale) or, with ``asymmetric``, (y, scale, offset)."""
+    _need_cuda(x, smooth_scales, group_index)
+    x = x.contiguous()
+    k = x.shape[-1]
+    rows = x.numel() // k if k else int(torch.Size(x.shape[:-1]).numel())
+    y = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    scale = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    offset = torch.empty_like(scale) if asymmetric else None
+    sm = None if smooth_scales is None else smooth_scales.contiguous()
+    gi = None if group_index is None else group_index.to(torch.int32).contiguous()
+    check(lib().b200q_dynamic_quant_ext(_ptr(x), DTYPE[x.dtype], _ptr(sm), NONE if sm is None else DTYPE[sm.dtype],
+                                        _ptr(gi), 0 if gi is None else gi.numel(), _ptr(y), _ptr(scale), _ptr(offset),
+                                        rows, k, _stream()))
+    return (y, scale, offset) if asymmetric else (y, scale)
+
+
+def anti_quant(x: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor | None = None,
+               dst_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """``b200q_anti_quant``: int8, or int32 words of eight int4 values, to fp16/bf16."""
+    _need_cuda(x, scale, offset)
+    x = x.contiguous()
+    bits = 4 if x.dtype == torch.int32 else 8
+    n = x.shape[-1] * (8 if bits == 4 else 1)
+    out = torch.empty((*x.shape[:-1], n), dtype=dst_dtype, device=x.device)
+    rows = out.numel() // n if n else 0
+    sc = scale.contiguous()
+    of = None if offset is None else offset.contiguous()
+    check(lib().b200q_anti_quant(_ptr(x), bits, _ptr(sc), _ptr(of), DTYPE[sc.dtype], _ptr(out), DTYPE[dst_dtype],
+                                 rows, n, _stream()))
+    return out
 
 
 def quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None, output_dtype=None,

@@ -3,7 +3,9 @@
 // without relocatable device code.
 #include "status.cu"
 #include "dynamic_quant.cu"
+#include "dynamic_quant_ext.cu"
 #include "int4pack.cu"
+#include "anti_quant.cu"
 #include "w8a8_gemm.cu"
 #include "w4a16_gemm.cu"
 #include "peer_scatter.cu"

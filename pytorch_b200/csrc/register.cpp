@@ -59,15 +59,23 @@ std::tuple<Tensor, Tensor> dynamic_quant_check(const Tensor& input, const option
   TORCH_CHECK(input.dim() >= 1, "npu_dynamic_quant: input must have at least one dimension");
   TORCH_CHECK(input.scalar_type() == at::kBFloat16 || input.scalar_type() == at::kHalf,
               "npu_dynamic_quant: input must be float16 or bfloat16, got ", input.scalar_type());
-  TORCH_CHECK(!group_index.has_value(), "npu_dynamic_quant: group_index (per-expert smooth scales) is not supported");
   TORCH_CHECK(!dst_type.has_value() || *dst_type == at::kChar,
               "npu_dynamic_quant: dst_type must be torch.int8, got ", *dst_type);
-  if (smooth.has_value()) {
+  if (group_index.has_value()) {
+    // One smooth-scale row per group of tokens (test/onnx/test_wrapper_onnx_ops.py:1345-1354).
+    TORCH_CHECK(smooth.has_value(), "npu_dynamic_quant: group_index needs smooth_scales of shape [groups, k]");
+    TORCH_CHECK(group_index->dim() == 1 && (group_index->scalar_type() == at::kInt || group_index->scalar_type() == at::kLong),
+                "npu_dynamic_quant: group_index must be a 1-D int32 or int64 tensor");
+    TORCH_CHECK(smooth->dim() == 2 && smooth->size(0) == group_index->size(0) && smooth->size(1) == input.size(-1),
+                "npu_dynamic_quant: with group_index, smooth_scales must have shape [", group_index->size(0), ", ",
+                input.size(-1), "]");
+  } else if (smooth.has_value()) {
     TORCH_CHECK(smooth->dim() == 1 && smooth->size(0) == input.size(-1),
                 "npu_dynamic_quant: smooth_scales must have shape [", input.size(-1), "]");
+  }
+  if (smooth.has_value())
     TORCH_CHECK(smooth->scalar_type() == at::kFloat || smooth->scalar_type() == input.scalar_type(),
                 "npu_dynamic_quant: smooth_scales must be float32 or the input's dtype");
-  }
   auto scale_shape = input.sizes().vec();
   scale_shape.pop_back();
   return {at::empty(input.sizes(), input.options().dtype(at::kChar)),
@@ -84,12 +92,103 @@ std::tuple<Tensor, Tensor> dynamic_quant_cuda(const Tensor& input, const optiona
   Tensor sm = smooth.has_value() ? smooth->contiguous() : Tensor();
   const int64_t k = x.size(-1);
   const int64_t rows = k ? x.numel() / k : scale.numel();
+  if (group_index.has_value()) {
+    Tensor gi = group_index->to(at::kInt).contiguous();
+    check_status(b200q_dynamic_quant_ext(x.data_ptr(), dtype_enum(x.scalar_type()), sm.data_ptr(),
+                                         dtype_enum(sm.scalar_type()), static_cast<const int32_t*>(gi.data_ptr()),
+                                         gi.numel(), static_cast<int8_t*>(y.data_ptr()),
+                                         static_cast<float*>(scale.data_ptr()), nullptr, rows, k, stream_of(x)),
+                 "npu_dynamic_quant");
+    return {y, scale};
+  }
   check_status(b200q_dynamic_quant(x.data_ptr(), dtype_enum(x.scalar_type()), sm.defined() ? sm.data_ptr() : nullptr,
                                    sm.defined() ? dtype_enum(sm.scalar_type()) : B200Q_NONE,
                                    static_cast<int8_t*>(y.data_ptr()), static_cast<float*>(scale.data_ptr()), rows, k,
                                    stream_of(x)),
                "npu_dynamic_quant");
   return {y, scale};
+}
+
+// npu_dynamic_quant_asymmetric(input, *, smooth_scales=None, group_index=None, dst_type=None) -> (y, scale, offset)
+std::tuple<Tensor, Tensor, Tensor> dynamic_quant_asym_cuda(const Tensor& input, const optional<Tensor>& smooth,
+                                                           const optional<Tensor>& group_index,
+                                                           optional<at::ScalarType> dst_type) {
+  check_same_device("npu_dynamic_quant_asymmetric", input, {&smooth, &group_index});
+  c10::cuda::CUDAGuard guard(input.device());
+  auto [y, scale] = dynamic_quant_check(input, smooth, group_index, dst_type);
+  Tensor offset = at::empty_like(scale);
+  Tensor x = input.contiguous();
+  Tensor sm = smooth.has_value() ? smooth->contiguous() : Tensor();
+  Tensor gi = group_index.has_value() ? group_index->to(at::kInt).contiguous() : Tensor();
+  const int64_t k = x.size(-1);
+  const int64_t rows = k ? x.numel() / k : scale.numel();
+  check_status(b200q_dynamic_quant_ext(x.data_ptr(), dtype_enum(x.scalar_type()), sm.defined() ? sm.data_ptr() : nullptr,
+                                       sm.defined() ? dtype_enum(sm.scalar_type()) : B200Q_NONE,
+                                       gi.defined() ? static_cast<const int32_t*>(gi.data_ptr()) : nullptr,
+                                       gi.defined() ? gi.numel() : 0, static_cast<int8_t*>(y.data_ptr()),
+                                       static_cast<float*>(scale.data_ptr()), static_cast<float*>(offset.data_ptr()),
+                                       rows, k, stream_of(x)),
+               "npu_dynamic_quant_asymmetric");
+  return {y, scale, offset};
+}
+
+std::tuple<Tensor, Tensor, Tensor> dynamic_quant_asym_meta(const Tensor& input, const optional<Tensor>& smooth,
+                                                           const optional<Tensor>& group_index,
+                                                           optional<at::ScalarType> dst_type) {
+  auto [y, scale] = dynamic_quant_check(input, smooth, group_index, dst_type);
+  return {y, scale, at::empty_like(scale)};
+}
+
+// ---------------------------------------------------------------------------------------------
+// npu_anti_quant(x, scale, *, offset=None, dst_dtype=None, src_dtype=None) -> Tensor
+// x int8 [..., n], or int32 words of eight int4 values [..., n/8]; scale/offset [n] float32 or bfloat16.
+std::vector<int64_t> anti_quant_check(const Tensor& x, const Tensor& scale, const optional<Tensor>& offset,
+                                      optional<at::ScalarType> dst_dtype, optional<at::ScalarType> src_dtype) {
+  TORCH_CHECK(x.scalar_type() == at::kChar || x.scalar_type() == at::kInt,
+              "npu_anti_quant: x must be int8, or int32 holding eight int4 values per element, got ", x.scalar_type());
+  TORCH_CHECK(x.dim() >= 1, "npu_anti_quant: x must have at least one dimension");
+  TORCH_CHECK(!dst_dtype.has_value() || *dst_dtype == at::kHalf || *dst_dtype == at::kBFloat16,
+              "The argument 'dst_dtype' must be torch.float16 or torch.bfloat16.");
+  TORCH_CHECK(!src_dtype.has_value() || *src_dtype == at::kChar || *src_dtype == at::kQUInt4x2,
+              "The argument 'src_dtype' must be torch.int8 or torch.quint4x2.");
+  auto shape = x.sizes().vec();
+  if (x.scalar_type() == at::kInt) shape.back() *= 8;
+  TORCH_CHECK(scale.scalar_type() == at::kFloat || scale.scalar_type() == at::kBFloat16,
+              "npu_anti_quant: scale must be float32 or bfloat16, got ", scale.scalar_type());
+  TORCH_CHECK(scale.numel() == shape.back() || scale.numel() == 1, "npu_anti_quant: scale must have ", shape.back(),
+              " elements (or one), got ", scale.numel());
+  if (offset.has_value()) {
+    TORCH_CHECK(offset->scalar_type() == scale.scalar_type(), "npu_anti_quant: offset must have the dtype of scale");
+    TORCH_CHECK(offset->numel() == scale.numel(), "npu_anti_quant: offset must have the shape of scale");
+  }
+  return shape;
+}
+
+Tensor anti_quant_cuda(const Tensor& x, const Tensor& scale, const optional<Tensor>& offset,
+                       optional<at::ScalarType> dst_dtype, optional<at::ScalarType> src_dtype) {
+  check_same_device("npu_anti_quant", x, {&offset});
+  TORCH_CHECK(scale.device() == x.device(), "Expected all tensors to be on the same device, but found at least two devices, ",
+              x.device(), " and ", scale.device(), "! (npu_anti_quant)");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto shape = anti_quant_check(x, scale, offset, dst_dtype, src_dtype);
+  const at::ScalarType out_t = dst_dtype.value_or(at::kHalf);
+  Tensor out = at::empty(shape, x.options().dtype(out_t));
+  const int64_t n = shape.back();
+  const int64_t rows = n ? out.numel() / n : 0;
+  Tensor xc = x.contiguous();
+  Tensor sc = (scale.numel() == n ? scale : scale.expand({n})).contiguous();
+  Tensor of = offset.has_value() ? (offset->numel() == n ? *offset : offset->expand({n})).contiguous() : Tensor();
+  check_status(b200q_anti_quant(xc.data_ptr(), x.scalar_type() == at::kInt ? 4 : 8, sc.data_ptr(),
+                                of.defined() ? of.data_ptr() : nullptr, dtype_enum(sc.scalar_type()), out.data_ptr(),
+                                dtype_enum(out_t), rows, n, stream_of(x)),
+               "npu_anti_quant");
+  return out;
+}
+
+Tensor anti_quant_meta(const Tensor& x, const Tensor& scale, const optional<Tensor>& offset,
+                       optional<at::ScalarType> dst_dtype, optional<at::ScalarType> src_dtype) {
+  auto shape = anti_quant_check(x, scale, offset, dst_dtype, src_dtype);
+  return at::empty(shape, x.options().dtype(dst_dtype.value_or(at::kHalf)));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -380,6 +479,10 @@ TORCH_LIBRARY(npu, m) {
         "Tensor? quant_scale=None, Tensor? quant_offset=None, Tensor? bias=None, int antiquant_group_size=0, "
         "int inner_precise=0, *, ScalarType? weight_dtype=None) -> Tensor");
   m.def("npu_convert_weight_to_int4pack(Tensor weight, int inner_k_tiles=0) -> Tensor");
+  m.def("npu_dynamic_quant_asymmetric(Tensor input, *, Tensor? smooth_scales=None, Tensor? group_index=None, "
+        "ScalarType? dst_type=None) -> (Tensor, Tensor, Tensor)");
+  m.def("npu_anti_quant(Tensor x, Tensor scale, *, Tensor? offset=None, ScalarType? dst_dtype=None, "
+        "ScalarType? src_dtype=None) -> Tensor");
   m.def("npu_trans_quant_param(Tensor scale, Tensor? offset=None) -> Tensor");
 }
 
@@ -388,6 +491,8 @@ TORCH_LIBRARY_IMPL(npu, CUDA, m) {
   m.impl("npu_quant_matmul", TORCH_FN(quant_matmul_cuda));
   m.impl("npu_weight_quant_batchmatmul", TORCH_FN(weight_quant_cuda));
   m.impl("npu_convert_weight_to_int4pack", TORCH_FN(int4pack_cuda));
+  m.impl("npu_dynamic_quant_asymmetric", TORCH_FN(dynamic_quant_asym_cuda));
+  m.impl("npu_anti_quant", TORCH_FN(anti_quant_cuda));
   m.impl("npu_trans_quant_param", TORCH_FN(trans_quant_param_cuda));
 }
 
@@ -396,5 +501,7 @@ TORCH_LIBRARY_IMPL(npu, Meta, m) {
   m.impl("npu_quant_matmul", TORCH_FN(quant_matmul_meta));
   m.impl("npu_weight_quant_batchmatmul", TORCH_FN(weight_quant_meta));
   m.impl("npu_convert_weight_to_int4pack", TORCH_FN(int4pack_meta));
+  m.impl("npu_dynamic_quant_asymmetric", TORCH_FN(dynamic_quant_asym_meta));
+  m.impl("npu_anti_quant", TORCH_FN(anti_quant_meta));
   m.impl("npu_trans_quant_param", TORCH_FN(trans_quant_param_meta));
 }

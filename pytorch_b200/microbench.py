@@ -69,6 +69,40 @@ def bench_dq(m, k, iters, plain):
             "algorithmic_bytes": by}
 
 
+def bench_dq_asym(m, k, iters, plain):
+    lib = cabi.lib()
+    xs = [torch.randn(m, k, device="cuda", dtype=torch.bfloat16) for _ in range(min(_copies(m * k * 3), 64))]
+    sm = torch.rand(k, device="cuda") + 0.5
+    y = torch.empty(m, k, device="cuda", dtype=torch.int8)
+    s, o = torch.empty(m, device="cuda"), torch.empty(m, device="cuda")
+    calls = [(lambda sp, x=x: cabi.check(lib.b200q_dynamic_quant_ext(
+        x.data_ptr(), cabi.BF16, sm.data_ptr(), cabi.F32, None, 0, y.data_ptr(), s.data_ptr(), o.data_ptr(), m, k, sp)))
+        for x in xs]
+    ms = _graph_time(calls, iters, plain)
+    by = workloads.dynamic_quant_bytes(m, k) + 4 * m
+    return {"op": "dynamic_quant_asymmetric", "m": m, "k": k, "us": round(ms * 1e3, 2),
+            "gbs": round(by / ms / 1e6, 1), "algorithmic_bytes": by}
+
+
+def bench_anti_quant(m, n, bits, iters, plain):
+    lib = cabi.lib()
+    in_bytes = m * n * bits // 8
+    if bits == 8:
+        xs = [torch.randint(-128, 128, (m, n), device="cuda", dtype=torch.int8)
+              for _ in range(min(_copies(m * n * 3), 64))]
+    else:
+        xs = [torch.randint(-2 ** 31, 2 ** 31 - 1, (m, n // 8), device="cuda", dtype=torch.int32)
+              for _ in range(min(_copies(m * n * 3), 64))]
+    sc, of = torch.rand(n, device="cuda") + 0.5, torch.rand(n, device="cuda")
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    calls = [(lambda sp, x=x: cabi.check(lib.b200q_anti_quant(x.data_ptr(), bits, sc.data_ptr(), of.data_ptr(), cabi.F32,
+                                                              out.data_ptr(), cabi.BF16, m, n, sp))) for x in xs]
+    ms = _graph_time(calls, iters, plain)
+    by = in_bytes + 2 * m * n + 8 * n
+    return {"op": f"anti_quant_int{bits}", "m": m, "n": n, "us": round(ms * 1e3, 2), "gbs": round(by / ms / 1e6, 1),
+            "algorithmic_bytes": by}
+
+
 def bench_qmm(m, k, n, iters, plain):
     lib = cabi.lib()
     wts = [torch.randint(-127, 128, (n, k), device="cuda", dtype=torch.int8) for _ in range(min(_copies(k * n), 64))]
@@ -122,7 +156,8 @@ def bench_w4(m, k, n, gs, iters, plain):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["dq", "qmm", "w4", "suite"])
+    ap.add_argument("op", choices=["dq", "dqa", "aq", "qmm", "w4", "suite"])
+    ap.add_argument("--bits", type=int, default=8)
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
@@ -134,6 +169,10 @@ def main():
         raise SystemExit("microbench needs a CUDA device")
     if a.op == "dq":
         print(json.dumps(bench_dq(a.m, a.k, a.iters, a.plain)))
+    elif a.op == "dqa":
+        print(json.dumps(bench_dq_asym(a.m, a.k, a.iters, a.plain)))
+    elif a.op == "aq":
+        print(json.dumps(bench_anti_quant(a.m, a.n, a.bits, a.iters, a.plain)))
     elif a.op == "qmm":
         print(json.dumps(bench_qmm(a.m, a.k, a.n, a.iters, a.plain)))
     elif a.op == "w4":
@@ -146,6 +185,9 @@ def main():
                 print(json.dumps(bench_qmm(m, k, n, a.iters, a.plain)), flush=True)
         for m in workloads.C3_M:
             print(json.dumps(bench_w4(m, workloads.C3_K, workloads.C3_N, workloads.C3_GS, a.iters, a.plain)), flush=True)
+        print(json.dumps(bench_dq_asym(4096, 8192, a.iters, a.plain)), flush=True)
+        for bits in (8, 4):
+            print(json.dumps(bench_anti_quant(8192, 8192, bits, a.iters, a.plain)), flush=True)
         print(json.dumps({"device_error": cabi.device_error()}))
 
 

@@ -9,7 +9,8 @@ a machine without an Ascend device) and executed unchanged on small seeded
 inputs.  The tests then require the oracle to reproduce those outputs:
 
 * ``unpack_int4``                       test/custom_ops/test_npu_anti_quant.py:12-24
-* ``TestAntiQuant.custom_op_exec``      test/custom_ops/test_npu_anti_quant.py:29-42
+* ``TestAntiQuant.custom_op_exec``      test/custom_ops/test_npu_anti_quant.py:29-42 (int4 and int8 inputs,
+                                        fp16 and bf16 outputs, with and without offset)
 * ``cpu_linear_weight_quant``           test/contrib/test_linear_weight_quant.py:20-28
 * ``_get_global_tensor`` (int8 dequant) test/distributed/tensor/test_matrix_ops.py:21-40
 
@@ -70,6 +71,16 @@ def reference_goldens(ref):
     offs = torch.rand(80, generator=g) * 200 - 100
     out["anti_scale"], out["anti_offset"] = scale.numpy(), offs.numpy()
     out["anti_out_f16"] = ns["custom_op_exec"](None, packed, scale, offs, torch.float16, None).numpy()
+    # int8 input, both output types, with and without offset (shapes of test_npu_anti_quant.py:49-58)
+    g8 = torch.Generator().manual_seed(78)      # its own stream: the draws below keep their values
+    x8 = torch.randint(-127, 128, (10, 100), generator=g8, dtype=torch.int64).to(torch.int8)
+    sc8 = torch.rand(100, generator=g8) * 200 - 100
+    of8 = torch.rand(100, generator=g8) * 200 - 100
+    out["anti8_x"], out["anti8_scale"], out["anti8_offset"] = x8.numpy(), sc8.numpy(), of8.numpy()
+    out["anti8_out_f16"] = ns["custom_op_exec"](None, x8, sc8, of8, torch.float16, torch.int8).numpy()
+    out["anti8_out_bf16"] = bits(ns["custom_op_exec"](None, x8, sc8, of8, torch.bfloat16, torch.int8))
+    out["anti8_out_nooff_f16"] = ns["custom_op_exec"](None, x8, sc8, None, torch.float16, None).numpy()
+    out["anti_out_bf16"] = bits(ns["custom_op_exec"](None, packed, scale, offs, torch.bfloat16, None))
 
     ns2 = {"np": np, "torch": torch}
     f_wq = os.path.join(ref, "test/contrib/test_linear_weight_quant.py")

@@ -135,6 +135,29 @@ def test_weight_quant_and_pack_meta_contract(pkg):
         pkg.npu_convert_weight_to_int4pack(meta(4, 12, dtype=torch.int32))
 
 
+def test_sibling_ops_meta_contract(pkg):
+    # npu_dynamic_quant_asymmetric: test/test_fake_tensor.py:1690-1709
+    x = meta(4, 2048, 1024, dtype=torch.float16)
+    y, s, o = pkg.npu_dynamic_quant_asymmetric(x, smooth_scales=meta(1024, dtype=torch.float16))
+    assert y.shape == (4, 2048, 1024) and y.dtype == torch.int8
+    assert s.shape == (4, 2048) and s.dtype == torch.float32 and o.shape == (4, 2048) and o.dtype == torch.float32
+    # group_index: one smooth row per group (test/onnx/test_wrapper_onnx_ops.py:1335-1392)
+    y, s = pkg.npu_dynamic_quant(x, smooth_scales=meta(10, 1024, dtype=torch.float16),
+                                 group_index=meta(10, dtype=torch.int32))
+    assert y.shape == (4, 2048, 1024) and s.shape == (4, 2048)
+    with pytest.raises(RuntimeError, match="group_index"):
+        pkg.npu_dynamic_quant(x, smooth_scales=meta(1024, dtype=torch.float16), group_index=meta(10, dtype=torch.int32))
+    # npu_anti_quant: test/test_fake_tensor.py:1949-1959
+    q = meta(20, 100, dtype=torch.int8)
+    r = pkg.npu_anti_quant(q, meta(100, dtype=torch.float32), offset=meta(100, dtype=torch.float32),
+                           dst_dtype=torch.float16)
+    assert r.shape == q.shape and r.dtype == torch.float16
+    r = pkg.npu_anti_quant(meta(10, 25, dtype=torch.int32), meta(200, dtype=torch.float32), dst_dtype=torch.bfloat16)
+    assert r.shape == (10, 200) and r.dtype == torch.bfloat16
+    with pytest.raises(RuntimeError, match="dst_dtype"):
+        pkg.npu_anti_quant(q, meta(100, dtype=torch.float32), dst_dtype=torch.float32)
+
+
 def test_trans_quant_param_meta_contract(pkg):
     r = pkg.npu_trans_quant_param(meta(1, dtype=torch.float32), meta(4, dtype=torch.float32))
     assert r.shape == (4,) and r.dtype == torch.int64
