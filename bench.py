@@ -246,8 +246,11 @@ def run_b200(args):
         step(d["x"], d["x_down"])
     barrier()
     barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
+    # Only the rank that prints the line samples its GPU: eight processes polling NVML at this rate
+    # would contend with each other's kernel launches.
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler is not None:
+        sampler.start()
     t0, t1 = ev(), ev()
     t0.record()
     host_t0 = time.perf_counter()
@@ -257,7 +260,7 @@ def run_b200(args):
     host_ms_step = (time.perf_counter() - host_t0) * 1e3 / args.steps     # time the host needs to launch one step
     barrier()
     ms_total = max_over_ranks(t0.elapsed_time(t1))
-    clocks = sampler.stop()
+    clocks = sampler.stop() if sampler is not None else None
     if plans is not None:
         # per-kernel events from three extra steps through the event-recording path (same kernels, same buffers)
         for _ in range(3):

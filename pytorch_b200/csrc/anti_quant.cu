@@ -65,39 +65,71 @@ __device__ __forceinline__ float aq_one(float x, float sc, float of, bool has_of
   return __fmul_rn(has_off ? __fadd_rn(x, of) : x, sc);
 }
 
-// Vector path: n % 16 == 0, all buffers 16-byte aligned.  One thread produces 16 consecutive
-// outputs of one row: int8 from one 128-bit load, int4 from one 64-bit load (value j of a word in
-// bits [4j, 4j+4), sign-extended).
+// Integers placed in the mantissa of 2^23 and one exact subtraction: cheaper than the
+// quarter-rate integer-to-float conversion.  int8: byte b of the word, biased by 128.
+__device__ __forceinline__ float aq_byte_to_float(uint32_t w_biased, int b) {
+  // selector 0x7440 | b: result bytes (b, 4, 4, 7) of {w_biased, 0x4B000000} = 0x4B0000bb
+  return __fsub_rn(__uint_as_float(__byte_perm(w_biased, 0x4B000000u, 0x7440 | b)), 8388736.0f);
+}
+__device__ __forceinline__ float aq_nibble_to_float(uint32_t w_biased, int j) {
+  return __fsub_rn(__uint_as_float(((w_biased >> (4 * j)) & 0xFu) | 0x4B000000u), 8388616.0f);
+}
+
+// Vector path: n % 16 == 0, all buffers 16-byte aligned.  A thread owns 16 consecutive columns
+// (its scale and offset values stay in registers) and walks down the rows: per row one 128-bit
+// (int8) or 64-bit (int4, value j of a word in bits [4j, 4j+4)) load and two 128-bit stores, the
+// loads of UNROLL rows issued before the first use so that enough bytes are in flight to cover
+// the HBM latency.  Without an offset the sum adds 0.0, which leaves the integer unchanged.
 template <int BITS, typename PT, typename OT>
-__global__ void __launch_bounds__(256) anti_quant_vec_kernel(const void* __restrict__ x, const PT* __restrict__ scale,
-                                                             const PT* __restrict__ offset, OT* __restrict__ out,
-                                                             int64_t nvec, int vec_per_row) {
-  const bool has_off = offset != nullptr;
-  for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t c0 = (v % vec_per_row) * 16;
-    float f[16];
-    if (BITS == 8) {
-      const uint4 q = __ldcs(static_cast<const uint4*>(x) + v);
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+__global__ void __launch_bounds__(256, 3) anti_quant_vec_kernel(const void* __restrict__ x, const PT* __restrict__ scale,
+                                                                const PT* __restrict__ offset, OT* __restrict__ out,
+                                                                int64_t rows, int vec_per_row) {
+  constexpr int UNROLL = 4;
+  const int cv = blockIdx.x * blockDim.x + threadIdx.x;
+  if (cv >= vec_per_row) return;
+  float sc[16], of[16];
+  aq_load16(scale + cv * 16, sc);
+  if (offset != nullptr) {
+    aq_load16(offset + cv * 16, of);
+  } else {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) f[j] = (float)(int8_t)(w[j >> 2] >> (8 * (j & 3)));
-    } else {
-      const uint2 q = __ldcs(static_cast<const uint2*>(x) + v);
-      const uint32_t w[2] = {q.x, q.y};
+    for (int j = 0; j < 16; ++j) of[j] = 0.0f;
+  }
+  const int64_t rstep = gridDim.y;
+  for (int64_t r0 = blockIdx.y; r0 < rows; r0 += rstep * UNROLL) {
+    uint4 q[UNROLL];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) f[j] = (float)(((int32_t)(w[j >> 3] << (28 - 4 * (j & 7)))) >> 28);
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t r = r0 + u * rstep;
+      q[u] = make_uint4(0, 0, 0, 0);
+      if (r < rows) {
+        const int64_t v = r * vec_per_row + cv;
+        if (BITS == 8) q[u] = __ldcs(static_cast<const uint4*>(x) + v);
+        else { const uint2 t = __ldcs(static_cast<const uint2*>(x) + v); q[u].x = t.x; q[u].y = t.y; }
+      }
     }
-    float sc[16], of[16];
-    aq_load16(scale + c0, sc);
-    if (has_off) aq_load16(offset + c0, of);
-    uint32_t o[8];
 #pragma unroll
-    for (int j = 0; j < 16; j += 2)
-      o[j >> 1] = aq_pack<OT>(aq_one(f[j], sc[j], has_off ? of[j] : 0.0f, has_off),
-                              aq_one(f[j + 1], sc[j + 1], has_off ? of[j + 1] : 0.0f, has_off));
-    uint4* dst = reinterpret_cast<uint4*>(out) + 2 * v;
-    __stcs(dst, make_uint4(o[0], o[1], o[2], o[3]));
-    __stcs(dst + 1, make_uint4(o[4], o[5], o[6], o[7]));
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t r = r0 + u * rstep;
+      if (r >= rows) break;
+      uint32_t o[8];
+      if (BITS == 8) {
+        const uint32_t w[4] = {q[u].x ^ 0x80808080u, q[u].y ^ 0x80808080u, q[u].z ^ 0x80808080u, q[u].w ^ 0x80808080u};
+#pragma unroll
+        for (int j = 0; j < 16; j += 2)
+          o[j >> 1] = aq_pack<OT>(__fmul_rn(__fadd_rn(aq_byte_to_float(w[j >> 2], j & 3), of[j]), sc[j]),
+                                  __fmul_rn(__fadd_rn(aq_byte_to_float(w[j >> 2], (j & 3) + 1), of[j + 1]), sc[j + 1]));
+      } else {
+        const uint32_t w[2] = {q[u].x ^ 0x88888888u, q[u].y ^ 0x88888888u};
+#pragma unroll
+        for (int j = 0; j < 16; j += 2)
+          o[j >> 1] = aq_pack<OT>(__fmul_rn(__fadd_rn(aq_nibble_to_float(w[j >> 3], j & 7), of[j]), sc[j]),
+                                  __fmul_rn(__fadd_rn(aq_nibble_to_float(w[j >> 3], (j & 7) + 1), of[j + 1]), sc[j + 1]));
+      }
+      uint4* dst = reinterpret_cast<uint4*>(out) + 2 * (r * vec_per_row + cv);
+      __stcs(dst, make_uint4(o[0], o[1], o[2], o[3]));
+      __stcs(dst + 1, make_uint4(o[4], o[5], o[6], o[7]));
+    }
   }
 }
 
@@ -127,12 +159,17 @@ int launch_anti_quant(const void* x, const void* scale, const void* offset, void
   const bool vec = n % 16 == 0 && aligned(x, 16) && aligned(out, 16) && aligned(scale, 16) &&
                    (offset == nullptr || aligned(offset, 16));
   if (vec) {
-    const int64_t nvec = total / 16;
-    const int64_t want = ceil_div(nvec, 256);
-    const int blocks = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
-    anti_quant_vec_kernel<BITS, PT, OT><<<blocks, 256, 0, st>>>(x, static_cast<const PT*>(scale),
-                                                                 static_cast<const PT*>(offset), static_cast<OT*>(out),
-                                                                 nvec, (int)(n / 16));
+    const int vpr = (int)(n / 16);
+    const int threads = vpr >= 256 ? 256 : (int)ceil_div(vpr, 32) * 32;
+    const unsigned gx = (unsigned)ceil_div(vpr, threads);
+    // about three CTAs of 256 threads per SM; every CTA takes at least UNROLL rows
+    int64_t gy = ceil_div((int64_t)sm_count() * 3 * 256, (int64_t)gx * threads);
+    const int64_t max_gy = ceil_div(rows, 4);
+    if (gy > max_gy) gy = max_gy;
+    if (gy > 65535) gy = 65535;
+    if (gy < 1) gy = 1;
+    anti_quant_vec_kernel<BITS, PT, OT><<<dim3(gx, (unsigned)gy), threads, 0, st>>>(
+        x, static_cast<const PT*>(scale), static_cast<const PT*>(offset), static_cast<OT*>(out), rows, vpr);
     return check_launch("anti_quant");
   }
   const int64_t want = ceil_div(total, 256);

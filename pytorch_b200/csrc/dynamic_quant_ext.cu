@@ -7,7 +7,8 @@
 // offset = 127 - max(xs) / scale, y = clamp(rint(xs / scale + offset), -128, 127);
 // a constant row gives scale 0, offset 0 and y 0.  The fast path forms fma(xs, 1/scale, offset)
 // and redoes a vector with IEEE division and a separate sum only when one of its values lies
-// within 1e-3 of a rounding boundary, where the two could round differently.
+// within 1e-4 of a rounding boundary, where the two could round differently (they differ by less
+// than 4e-5: |xs/scale| <= 255, three roundings of 2^-24 relative each).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -61,7 +62,7 @@ __device__ __forceinline__ uint2 quantize8_asym(const float (&f)[8], float scale
     dist = fmaxf(dist, fabsf(__fsub_rn(t, __fsub_rn(uf, kMagic))));
     u[j] = __float_as_uint(uf);
   }
-  if (dist > 0.499f || scale == 0.0f) {
+  if (dist > 0.4999f || scale == 0.0f) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) u[j] = scale == 0.0f ? 0u : (uint32_t)quant_asym_exact(f[j], scale, offset);
   }
@@ -77,41 +78,43 @@ __device__ __forceinline__ int group_of_row(const int32_t* __restrict__ gidx, in
 }
 
 template <typename T, typename ST, int ITERS, bool ASYM>
-__global__ void __launch_bounds__(ITERS <= 4 ? 1024 : 512)
+__global__ void __launch_bounds__(512)
 dynamic_quant_ext_rows(const T* __restrict__ x, const ST* __restrict__ smooth, const int32_t* __restrict__ gidx,
                        int ngroups, int8_t* __restrict__ y, float* __restrict__ scale_out,
                        float* __restrict__ offset_out, int64_t rows, int k) {
   __shared__ uint32_t red[2][64];
   const int nvec = k >> 3;
-  int par = 0;
-  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, par ^= 1) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + row * k) + threadIdx.x;
-    uint4 raw[ITERS];
+  uint4 raw[ITERS];
+  // A thread's vector past the end of the row is replaced by the row's last vector: it adds nothing
+  // new to the maximum and minimum, needs no predicates in the arithmetic, and is not stored.
+  auto load_row = [&](int64_t row) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * k);
 #pragma unroll
-    for (int i = 0; i < ITERS; ++i)
-      raw[i] = threadIdx.x + i * blockDim.x < nvec ? ld_stream(xr + i * blockDim.x) : make_uint4(0, 0, 0, 0);
+    for (int i = 0; i < ITERS; ++i) raw[i] = ld_stream(xr + min((int)(threadIdx.x + i * blockDim.x), nvec - 1));
+  };
+  int par = 0;
+  if ((int64_t)blockIdx.x < rows) load_row(blockIdx.x);
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, par ^= 1) {
     const ST* sm_row = smooth;
     if (smooth != nullptr && gidx != nullptr) sm_row = smooth + (int64_t)group_of_row(gidx, ngroups, row) * k;
     float f[ITERS][8];
     float mx = -INFINITY, mn = INFINITY;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
-      const int v = threadIdx.x + i * blockDim.x;
-      const bool live = v < nvec;
+      const int v = min((int)(threadIdx.x + i * blockDim.x), nvec - 1);
       const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
       float sm[8];
-      if (smooth != nullptr && live) load_smooth8(sm_row + v * 8, sm);
+      if (smooth != nullptr) load_smooth8(sm_row + v * 8, sm);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 pr = unpack2<T>(w[j]);
-        f[i][2 * j] = (smooth != nullptr && live) ? __fmul_rn(pr.x, sm[2 * j]) : pr.x;
-        f[i][2 * j + 1] = (smooth != nullptr && live) ? __fmul_rn(pr.y, sm[2 * j + 1]) : pr.y;
-        if (live) {
-          mx = fmaxf(mx, fmaxf(f[i][2 * j], f[i][2 * j + 1]));
-          mn = fminf(mn, fminf(f[i][2 * j], f[i][2 * j + 1]));
-        }
+        f[i][2 * j] = smooth != nullptr ? __fmul_rn(pr.x, sm[2 * j]) : pr.x;
+        f[i][2 * j + 1] = smooth != nullptr ? __fmul_rn(pr.y, sm[2 * j + 1]) : pr.y;
+        mx = fmaxf(mx, fmaxf(f[i][2 * j], f[i][2 * j + 1]));
+        mn = fminf(mn, fminf(f[i][2 * j], f[i][2 * j + 1]));
       }
     }
+    if (row + gridDim.x < rows) load_row(row + gridDim.x);   // in flight during the reduction and quantisation
     block_max_min(mx, mn, red[par]);
     uint2* yr = reinterpret_cast<uint2*>(y + row * k) + threadIdx.x;
     if (ASYM) {
@@ -185,7 +188,7 @@ int launch_dq_ext(const void* x, const void* smooth, const int32_t* gidx, int ng
   const int nvec = (int)(k / 8);
   int iters = 1;
   while (iters < 4 && nvec > iters * 256) iters *= 2;
-  if (nvec > 4 * 1024)
+  if (nvec > 4 * 512)                                    // at most 512 threads: the row's fp32 products need the registers
     while (iters < 16 && nvec > iters * 512) iters *= 2;
   int threads = (int)ceil_div(nvec, iters);
   threads = (int)ceil_div(threads, 32) * 32;
