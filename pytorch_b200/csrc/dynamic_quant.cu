@@ -6,7 +6,7 @@
 // 2 B in + 1 B out per element.  The row maximum is a warp-shuffle reduction followed by
 // one exchange through shared memory.  Quantisation is bit-exact with
 // rint(xs / scale) under IEEE division: the fast path multiplies by 1/scale and only a
-// vector with an element within 2.5e-4 of a rounding boundary (where the two could differ)
+// vector with an element within 1e-4 of a rounding boundary (where the two could differ)
 // is redone with a true division.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -67,9 +67,10 @@ __device__ __forceinline__ void load_smooth8(const ST* p, float (&s)[8]) {
 // Eight values -> eight int8 (packed), bit-exact with clamp(rint(xs / scale)).
 // Fast path: fma(xs, 1/scale, 1.5 * 2^23) rounds the product to the nearest-even integer and leaves
 // its two's-complement low byte in the low mantissa byte (|xs/scale| <= 127.0001 because
-// scale = amax/127, so no clamp is needed).  The product can differ from the IEEE quotient by about
-// 2e-5, so the two can only round differently when it lies within 2.5e-4 of a half-integer: such a
-// vector is redone with IEEE division.
+// scale = amax/127, so no clamp is needed).  The product can differ from the IEEE quotient by at most
+// 1.2e-5 (127 * 2^-24 from the reciprocal, 2^-18 from the quotient's own rounding), so the two can
+// only round differently when it lies within that distance of a half-integer: a vector with a value
+// within 1e-4 of one is redone with IEEE division (about one warp instruction in twenty).
 __device__ __forceinline__ uint2 quantize8(const float (&f)[8], float scale, float inv) {
   constexpr float kMagic = 12582912.0f;
   uint32_t u[8];
@@ -81,7 +82,7 @@ __device__ __forceinline__ uint2 quantize8(const float (&f)[8], float scale, flo
     dist = fmaxf(dist, fabsf(__fmaf_rn(f[j], inv, -t)));
     u[j] = __float_as_uint(uf);
   }
-  if (dist > 0.49975f) {
+  if (dist > 0.4999f) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) u[j] = (uint32_t)__float2int_rn(__fdiv_rn(f[j], scale));
   }
