@@ -245,12 +245,13 @@ def run_b200(args):
     for _ in range(args.warmup):
         step(d["x"], d["x_down"])
     barrier()
-    barrier()
     # Only the rank that prints the line samples its GPU: eight processes polling NVML at this rate
-    # would contend with each other's kernel launches.
+    # would contend with each other's kernel launches.  The sampler is set up before the last barrier,
+    # so that the rank that pays for the NVML start-up does not enter the timed region late.
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler is not None:
         sampler.start()
+    barrier()
     t0, t1 = ev(), ev()
     t0.record()
     host_t0 = time.perf_counter()
