@@ -73,6 +73,15 @@ int b200q_dynamic_quant_ext(const void* x, int x_dtype, const void* smooth, int 
                             const int32_t* group_index, int64_t n_groups, int8_t* y, float* scale, float* offset,
                             int64_t rows, int64_t k, void* stream);
 
+/* npu_swiglu_quant(x, *, smooth_scales=None, ..., activate_left, quant_mode=1 (dynamic)) -> (int8 y, f32 scale)
+ *   replaces op_plugin::npu_swiglu_quant / aclnnSwiGluQuant (named in docs/zh/release_notes.md:303; the
+ *   activation is the reference's npu_swiglu, torch_npu/_inductor/decomposition.py:186-188).
+ * x [rows, 2f] bf16 or f16; act = silu(a) * b in fp32 with a = x[:, :f] when activate_left, else x[:, f:];
+ * xs = act * smooth (smooth [f], f32 or x's dtype, or NULL); then per row scale = max|xs| / 127,
+ * y = clamp(rint(xs / scale), -128, 127) as b200q_dynamic_quant.  f must be a multiple of 8, at most 32768. */
+int b200q_swiglu_quant(const void* x, int x_dtype, const void* smooth, int smooth_dtype, int activate_left,
+                       int8_t* y, float* scale, int64_t rows, int64_t f, void* stream);
+
 /* npu_quant_matmul(x1, x2, scale, *, offset, pertoken_scale, bias, output_dtype)
  *   replaces op_plugin::npu_quant_matmul / aclnnQuantMatmulV3-V4, reached from
  *   torch_npu/contrib/module/linear_quant.py:110-112 and linear_a8w8_quant.py:117-120.

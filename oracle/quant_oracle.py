@@ -111,6 +111,24 @@ def dynamic_quant_asymmetric(x, smooth_scales=None, group_index=None):
     return torch.from_numpy(y), torch.from_numpy(scale), torch.from_numpy(offset)
 
 
+def swiglu_quant(x, smooth_scales=None, activate_left=True):
+    """``npu_swiglu_quant`` in dynamic mode -> (int8 y, fp32 scale): ``act = silu(a) * b`` in fp32 with
+    ``a, b`` the halves of the last dimension (``a`` the left one when ``activate_left``; the reference's
+    ``npu_swiglu`` activates the left half: ``torch_npu/_inductor/decomposition.py:186-188``), then
+    ``act * smooth`` and the per-token quantisation of :func:`dynamic_quant`.  PARITY UNPINNED: the fused
+    operator is only named in the reference tree (``docs/zh/release_notes.md:303``).  ``exp`` is the
+    platform's fp32 one, so a GPU result is compared with a tolerance, not bit for bit."""
+    xf = _to_f32(x)
+    f = xf.shape[-1] // 2
+    a, b = (xf[..., :f], xf[..., f:]) if activate_left else (xf[..., f:], xf[..., :f])
+    with np.errstate(over="ignore"):
+        s = (F32(1.0) / (F32(1.0) + np.exp(-a).astype(F32))).astype(F32)
+    act = ((a * s).astype(F32) * b).astype(F32)
+    if smooth_scales is not None:
+        act = (act * _to_f32(smooth_scales)).astype(F32)
+    return dynamic_quant(torch.from_numpy(np.ascontiguousarray(act)))
+
+
 def anti_quant(x, scale, offset=None, dst_dtype=torch.float16, src_dtype=None):
     """``npu_anti_quant(x, scale, offset=None, dst_dtype, src_dtype)``: int8, or int32 words of eight
     int4 values, to fp16/bf16: ``cast((float(x) + offset) * scale)`` with an fp32 sum and an fp32

@@ -25,6 +25,7 @@ OPS = (
     "npu_trans_quant_param",
     "npu_dynamic_quant_asymmetric",
     "npu_anti_quant",
+    "npu_swiglu_quant",
 )
 
 
@@ -45,6 +46,7 @@ npu_convert_weight_to_int4pack = _torch.ops.npu.npu_convert_weight_to_int4pack
 npu_trans_quant_param = _torch.ops.npu.npu_trans_quant_param
 npu_dynamic_quant_asymmetric = _torch.ops.npu.npu_dynamic_quant_asymmetric
 npu_anti_quant = _torch.ops.npu.npu_anti_quant
+npu_swiglu_quant = _torch.ops.npu.npu_swiglu_quant
 
 from . import contrib  # noqa: E402,F401
 

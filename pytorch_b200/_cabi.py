@@ -26,6 +26,7 @@ EXPORTS = (
     "b200q_static_scratch_bytes", "b200q_quant_matmul_static_scratch",
     "b200q_weight_quant_matmul_workspace_bytes", "b200q_weight_quant_matmul", "b200q_int4pack",
     "b200q_trans_quant_param", "b200q_scatter_columns", "b200q_dynamic_quant_ext", "b200q_anti_quant",
+    "b200q_swiglu_quant",
 )
 
 
@@ -95,6 +96,8 @@ def lib() -> C.CDLL:
         l.b200q_trans_quant_param.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p]
         l.b200q_dynamic_quant_ext.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int64,
                                               C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+        l.b200q_swiglu_quant.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                         C.c_int64, C.c_int64, C.c_void_p]
         l.b200q_anti_quant.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
                                        C.c_int64, C.c_int64, C.c_void_p]
         l.b200q_scatter_columns.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int64, C.c_int64, C.c_int64,
@@ -159,6 +162,20 @@ def dynamic_quant_ext(x: torch.Tensor, smooth_scales: torch.Tensor | None = None
                                         _ptr(gi), 0 if gi is None else gi.numel(), _ptr(y), _ptr(scale), _ptr(offset),
                                         rows, k, _stream()))
     return (y, scale, offset) if asymmetric else (y, scale)
+
+
+def swiglu_quant(x: torch.Tensor, smooth_scales: torch.Tensor | None = None, activate_left: bool = True):
+    """``b200q_swiglu_quant``: silu(a) * b of the two halves of the last dimension, then per-token int8."""
+    _need_cuda(x, smooth_scales)
+    x = x.contiguous()
+    f = x.shape[-1] // 2
+    rows = x.numel() // (2 * f) if f else int(torch.Size(x.shape[:-1]).numel())
+    y = torch.empty((*x.shape[:-1], f), dtype=torch.int8, device=x.device)
+    scale = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    sm = None if smooth_scales is None else smooth_scales.contiguous()
+    check(lib().b200q_swiglu_quant(_ptr(x), DTYPE[x.dtype], _ptr(sm), NONE if sm is None else DTYPE[sm.dtype],
+                                   int(activate_left), _ptr(y), _ptr(scale), rows, f, _stream()))
+    return y, scale
 
 
 def anti_quant(x: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor | None = None,

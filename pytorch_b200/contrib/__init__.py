@@ -1,1 +1,2 @@
+from . import function  # noqa: F401
 from . import module  # noqa: F401

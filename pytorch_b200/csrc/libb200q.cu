@@ -4,6 +4,7 @@
 #include "status.cu"
 #include "dynamic_quant.cu"
 #include "dynamic_quant_ext.cu"
+#include "swiglu_quant.cu"
 #include "int4pack.cu"
 #include "anti_quant.cu"
 #include "w8a8_gemm.cu"

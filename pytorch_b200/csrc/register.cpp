@@ -140,6 +140,57 @@ std::tuple<Tensor, Tensor, Tensor> dynamic_quant_asym_meta(const Tensor& input, 
 }
 
 // ---------------------------------------------------------------------------------------------
+// npu_swiglu_quant(x, *, smooth_scales=None, offsets=None, group_index=None, activate_left=False, quant_mode=0,
+//                  group_list_type=0, dst_type=None) -> (y, scale); only the dynamic mode (quant_mode=1) is built.
+std::tuple<Tensor, Tensor> swiglu_quant_check(const Tensor& x, const optional<Tensor>& smooth,
+                                              const optional<Tensor>& offsets, const optional<Tensor>& group_index,
+                                              int64_t quant_mode, optional<at::ScalarType> dst_type) {
+  TORCH_CHECK(x.dim() >= 1 && x.size(-1) % 2 == 0, "npu_swiglu_quant: the last dimension of x must be even");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf,
+              "npu_swiglu_quant: x must be float16 or bfloat16, got ", x.scalar_type());
+  TORCH_CHECK(quant_mode == 1, "npu_swiglu_quant: only quant_mode=1 (dynamic, per token) is implemented, got ", quant_mode);
+  TORCH_CHECK(!offsets.has_value() && !group_index.has_value(),
+              "npu_swiglu_quant: offsets and group_index are not supported");
+  TORCH_CHECK(!dst_type.has_value() || *dst_type == at::kChar, "npu_swiglu_quant: dst_type must be torch.int8");
+  const int64_t f = x.size(-1) / 2;
+  if (smooth.has_value()) {
+    TORCH_CHECK(smooth->numel() == f, "npu_swiglu_quant: smooth_scales must have ", f, " elements");
+    TORCH_CHECK(smooth->scalar_type() == at::kFloat || smooth->scalar_type() == x.scalar_type(),
+                "npu_swiglu_quant: smooth_scales must be float32 or the input's dtype");
+  }
+  auto shape = x.sizes().vec();
+  shape.back() = f;
+  auto scale_shape = shape;
+  scale_shape.pop_back();
+  return {at::empty(shape, x.options().dtype(at::kChar)), at::empty(scale_shape, x.options().dtype(at::kFloat))};
+}
+
+std::tuple<Tensor, Tensor> swiglu_quant_cuda(const Tensor& x, const optional<Tensor>& smooth,
+                                             const optional<Tensor>& offsets, const optional<Tensor>& group_index,
+                                             bool activate_left, int64_t quant_mode, int64_t /*group_list_type*/,
+                                             optional<at::ScalarType> dst_type) {
+  check_same_device("npu_swiglu_quant", x, {&smooth, &offsets, &group_index});
+  c10::cuda::CUDAGuard guard(x.device());
+  auto [y, scale] = swiglu_quant_check(x, smooth, offsets, group_index, quant_mode, dst_type);
+  Tensor xc = x.contiguous();
+  Tensor sm = smooth.has_value() ? smooth->contiguous() : Tensor();
+  const int64_t f = xc.size(-1) / 2;
+  const int64_t rows = f ? xc.numel() / (2 * f) : scale.numel();
+  check_status(b200q_swiglu_quant(xc.data_ptr(), dtype_enum(xc.scalar_type()), sm.defined() ? sm.data_ptr() : nullptr,
+                                  sm.defined() ? dtype_enum(sm.scalar_type()) : B200Q_NONE, activate_left ? 1 : 0,
+                                  static_cast<int8_t*>(y.data_ptr()), static_cast<float*>(scale.data_ptr()), rows, f,
+                                  stream_of(x)),
+               "npu_swiglu_quant");
+  return {y, scale};
+}
+
+std::tuple<Tensor, Tensor> swiglu_quant_meta(const Tensor& x, const optional<Tensor>& smooth,
+                                             const optional<Tensor>& offsets, const optional<Tensor>& group_index,
+                                             bool, int64_t quant_mode, int64_t, optional<at::ScalarType> dst_type) {
+  return swiglu_quant_check(x, smooth, offsets, group_index, quant_mode, dst_type);
+}
+
+// ---------------------------------------------------------------------------------------------
 // npu_anti_quant(x, scale, *, offset=None, dst_dtype=None, src_dtype=None) -> Tensor
 // x int8 [..., n], or int32 words of eight int4 values [..., n/8]; scale/offset [n] float32 or bfloat16.
 std::vector<int64_t> anti_quant_check(const Tensor& x, const Tensor& scale, const optional<Tensor>& offset,
@@ -481,6 +532,9 @@ TORCH_LIBRARY(npu, m) {
   m.def("npu_convert_weight_to_int4pack(Tensor weight, int inner_k_tiles=0) -> Tensor");
   m.def("npu_dynamic_quant_asymmetric(Tensor input, *, Tensor? smooth_scales=None, Tensor? group_index=None, "
         "ScalarType? dst_type=None) -> (Tensor, Tensor, Tensor)");
+  m.def("npu_swiglu_quant(Tensor x, *, Tensor? smooth_scales=None, Tensor? offsets=None, Tensor? group_index=None, "
+        "bool activate_left=False, int quant_mode=0, int group_list_type=0, ScalarType? dst_type=None) "
+        "-> (Tensor, Tensor)");
   m.def("npu_anti_quant(Tensor x, Tensor scale, *, Tensor? offset=None, ScalarType? dst_dtype=None, "
         "ScalarType? src_dtype=None) -> Tensor");
   m.def("npu_trans_quant_param(Tensor scale, Tensor? offset=None) -> Tensor");
@@ -493,6 +547,7 @@ TORCH_LIBRARY_IMPL(npu, CUDA, m) {
   m.impl("npu_convert_weight_to_int4pack", TORCH_FN(int4pack_cuda));
   m.impl("npu_dynamic_quant_asymmetric", TORCH_FN(dynamic_quant_asym_cuda));
   m.impl("npu_anti_quant", TORCH_FN(anti_quant_cuda));
+  m.impl("npu_swiglu_quant", TORCH_FN(swiglu_quant_cuda));
   m.impl("npu_trans_quant_param", TORCH_FN(trans_quant_param_cuda));
 }
 
@@ -503,5 +558,6 @@ TORCH_LIBRARY_IMPL(npu, Meta, m) {
   m.impl("npu_convert_weight_to_int4pack", TORCH_FN(int4pack_meta));
   m.impl("npu_dynamic_quant_asymmetric", TORCH_FN(dynamic_quant_asym_meta));
   m.impl("npu_anti_quant", TORCH_FN(anti_quant_meta));
+  m.impl("npu_swiglu_quant", TORCH_FN(swiglu_quant_meta));
   m.impl("npu_trans_quant_param", TORCH_FN(trans_quant_param_meta));
 }

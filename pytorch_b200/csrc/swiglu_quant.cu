@@ -1,0 +1,151 @@
+// npu_swiglu_quant (dynamic mode): the step between the gate/up projection and the down projection
+// of a quantised MLP block in one pass.  x [rows, 2F] holds the two halves side by side;
+// act = silu(a) * b with a the activated half (npu_swiglu activates the left one:
+// torch_npu/_inductor/decomposition.py:186-188), xs = act * smooth, then the per-token symmetric
+// int8 quantisation of npu_dynamic_quant.  Unfused, the activation would be written as bf16 and read
+// back (4 B per output element); fused, the kernel reads 4 B and writes 1 B per output element and
+// the activation never leaves fp32 registers.  Same row-per-CTA structure as dynamic_quant.cu.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace b200q {
+namespace {
+
+__device__ __forceinline__ float silu_mul(float a, float b) {
+  // silu(a) = a / (1 + exp(-a)); exp(-a) = inf for very negative a gives a * 0
+  const float s = __fdiv_rn(1.0f, __fadd_rn(1.0f, __expf(-a)));
+  return __fmul_rn(__fmul_rn(a, s), b);
+}
+
+template <typename T, typename ST, int ITERS>
+__global__ void __launch_bounds__(512)
+swiglu_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth, int8_t* __restrict__ y,
+                  float* __restrict__ scale_out, int64_t rows, int f, int act_offset, int gate_offset) {
+  __shared__ float red[2][32];
+  const int nvec = f >> 3;
+  // Rows up to 16384 outputs wide keep the next row's packed loads in flight during the arithmetic of
+  // the current one; wider rows need the registers for the fp32 activations and load as they go.
+  constexpr bool PREFETCH = ITERS <= 4;
+  uint4 ra[PREFETCH ? ITERS : 1], rb[PREFETCH ? ITERS : 1];
+  // A thread's vector past the end of the row repeats the row's last vector (not stored).
+  auto load_row = [&](int64_t row) {
+    if (!PREFETCH) return;
+    const uint4* xa = reinterpret_cast<const uint4*>(x + row * 2 * f + act_offset);
+    const uint4* xb = reinterpret_cast<const uint4*>(x + row * 2 * f + gate_offset);
+#pragma unroll
+    for (int i = 0; i < (PREFETCH ? ITERS : 1); ++i) {
+      const int v = min((int)(threadIdx.x + i * blockDim.x), nvec - 1);
+      ra[i] = ld_stream(xa + v);
+      rb[i] = ld_stream(xb + v);
+    }
+  };
+  int par = 0;
+  if ((int64_t)blockIdx.x < rows) load_row(blockIdx.x);
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, par ^= 1) {
+    float act[ITERS][8];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      const int v = min((int)(threadIdx.x + i * blockDim.x), nvec - 1);
+      uint4 qa, qb;
+      if (PREFETCH) {
+        qa = ra[PREFETCH ? i : 0];
+        qb = rb[PREFETCH ? i : 0];
+      } else {
+        qa = ld_stream(reinterpret_cast<const uint4*>(x + row * 2 * f + act_offset) + v);
+        qb = ld_stream(reinterpret_cast<const uint4*>(x + row * 2 * f + gate_offset) + v);
+      }
+      const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w};
+      const uint32_t wb[4] = {qb.x, qb.y, qb.z, qb.w};
+      float sm[8];
+      if (smooth != nullptr) load_smooth8(smooth + v * 8, sm);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = unpack2<T>(wa[j]), b = unpack2<T>(wb[j]);
+        float v0 = silu_mul(a.x, b.x), v1 = silu_mul(a.y, b.y);
+        if (smooth != nullptr) { v0 = __fmul_rn(v0, sm[2 * j]); v1 = __fmul_rn(v1, sm[2 * j + 1]); }
+        act[i][2 * j] = v0;
+        act[i][2 * j + 1] = v1;
+        amax = fmaxf(amax, fmaxf(fabsf(v0), fabsf(v1)));
+      }
+    }
+    if (row + gridDim.x < rows) load_row(row + gridDim.x);   // in flight during the reduction and quantisation
+    amax = block_max(amax, red[par]);
+    const float scale = __fdiv_rn(amax, 127.0f);
+    if (threadIdx.x == 0) scale_out[row] = scale;
+    const float inv = scale == 0.0f ? 0.0f : __frcp_rn(scale);
+    uint2* yr = reinterpret_cast<uint2*>(y + row * f) + threadIdx.x;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i)
+      if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8(act[i], scale, inv));
+  }
+}
+
+template <typename T, typename ST>
+int launch_swiglu_quant(const void* x, const void* smooth, int8_t* y, float* scale, int64_t rows, int64_t f,
+                        bool activate_left, cudaStream_t st) {
+  const T* xp = static_cast<const T*>(x);
+  const ST* sp = static_cast<const ST*>(smooth);
+  const int nvec = (int)(f / 8);
+  int iters = 1;
+  while (iters < 4 && nvec > iters * 256) iters *= 2;
+  if (nvec > 4 * 512)
+    while (iters < 8 && nvec > iters * 512) iters *= 2;
+  int threads = (int)ceil_div(nvec, iters);
+  threads = (int)ceil_div(threads, 32) * 32;
+  const int act_off = activate_left ? 0 : (int)f, gate_off = activate_left ? (int)f : 0;
+  int per_sm = 1;
+#define B200Q_SGQ_CASE(I)                                                                                    \
+  case I: {                                                                                                  \
+    auto kern = swiglu_quant_rows<T, ST, I>;                                                                 \
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0);                                \
+    const int64_t cap = (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);                                     \
+    kern<<<(unsigned)(rows < cap ? rows : cap), threads, 0, st>>>(xp, sp, y, scale, rows, (int)f, act_off,   \
+                                                                  gate_off);                                 \
+  } break;
+  switch (iters) {
+    B200Q_SGQ_CASE(1)
+    B200Q_SGQ_CASE(2)
+    B200Q_SGQ_CASE(4)
+    B200Q_SGQ_CASE(8)
+  }
+#undef B200Q_SGQ_CASE
+  return check_launch("swiglu_quant");
+}
+
+}  // namespace
+}  // namespace b200q
+
+extern "C" int b200q_swiglu_quant(const void* x, int x_dtype, const void* smooth, int smooth_dtype, int activate_left,
+                                  int8_t* y, float* scale, int64_t rows, int64_t f, void* stream) {
+  using namespace b200q;
+  clear_error();
+  B200Q_REQUIRE(rows >= 0 && f >= 0, B200Q_ERR_BAD_ARG, "swiglu_quant: negative size");
+  B200Q_REQUIRE(x_dtype == B200Q_BF16 || x_dtype == B200Q_F16, B200Q_ERR_UNSUPPORTED,
+                "swiglu_quant: input must be bf16 or f16 (dtype enum %d)", x_dtype);
+  if (rows == 0) return B200Q_OK;
+  B200Q_REQUIRE(rows <= 0x7fffffffLL, B200Q_ERR_UNSUPPORTED, "swiglu_quant: more than 2^31-1 rows");
+  B200Q_REQUIRE(scale != nullptr, B200Q_ERR_BAD_ARG, "swiglu_quant: scale is NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (f == 0) {
+    cudaError_t e = cudaMemsetAsync(scale, 0, rows * sizeof(float), st);
+    return e == cudaSuccess ? B200Q_OK : fail(B200Q_ERR_LAUNCH, "swiglu_quant: %s", cudaGetErrorString(e));
+  }
+  B200Q_REQUIRE(x != nullptr && y != nullptr, B200Q_ERR_BAD_ARG, "swiglu_quant: x or y is NULL");
+  B200Q_REQUIRE(f % 8 == 0 && f <= 8 * 512 * 8, B200Q_ERR_UNSUPPORTED,
+                "swiglu_quant: the output width (%lld) must be a multiple of 8 and at most 32768", (long long)f);
+  B200Q_REQUIRE(aligned(x, 16) && aligned(y, 8) && aligned(scale, 4) && (smooth == nullptr || aligned(smooth, 16)),
+                B200Q_ERR_BAD_ARG, "swiglu_quant: x and smooth_scales must be 16-byte aligned, y 8-byte aligned");
+  B200Q_REQUIRE(smooth == nullptr || smooth_dtype == B200Q_F32 || smooth_dtype == x_dtype, B200Q_ERR_UNSUPPORTED,
+                "swiglu_quant: smooth_scales must be f32 or the input's dtype");
+  const bool sm_f32 = smooth == nullptr || smooth_dtype == B200Q_F32;
+  const bool left = activate_left != 0;
+  if (x_dtype == B200Q_BF16) {
+    if (sm_f32) return launch_swiglu_quant<__nv_bfloat16, float>(x, smooth, y, scale, rows, f, left, st);
+    return launch_swiglu_quant<__nv_bfloat16, __nv_bfloat16>(x, smooth, y, scale, rows, f, left, st);
+  }
+  if (sm_f32) return launch_swiglu_quant<__half, float>(x, smooth, y, scale, rows, f, left, st);
+  return launch_swiglu_quant<__half, __half>(x, smooth, y, scale, rows, f, left, st);
+}

@@ -156,6 +156,12 @@ def test_sibling_ops_meta_contract(pkg):
     assert r.shape == (10, 200) and r.dtype == torch.bfloat16
     with pytest.raises(RuntimeError, match="dst_dtype"):
         pkg.npu_anti_quant(q, meta(100, dtype=torch.float32), dst_dtype=torch.float32)
+    # npu_swiglu_quant (dynamic mode): the last dimension halves
+    y, s = pkg.npu_swiglu_quant(meta(4, 128, 57344, dtype=torch.bfloat16), smooth_scales=meta(28672, dtype=torch.float32),
+                                activate_left=True, quant_mode=1)
+    assert y.shape == (4, 128, 28672) and y.dtype == torch.int8 and s.shape == (4, 128) and s.dtype == torch.float32
+    with pytest.raises(RuntimeError, match="quant_mode"):
+        pkg.npu_swiglu_quant(meta(4, 64, dtype=torch.bfloat16))
 
 
 def test_trans_quant_param_meta_contract(pkg):

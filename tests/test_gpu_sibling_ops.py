@@ -129,3 +129,62 @@ def test_group_index_matches_oracle(pb, k):
     assert torch.equal(y.cpu(), yo) and torch.equal(s.cpu(), so) and torch.equal(o.cpu(), oo)
     with pytest.raises(RuntimeError, match="group_index"):
         pb.npu_dynamic_quant(x.cuda(), group_index=gi.cuda())
+
+
+def close_int8(got, want, scale_got, scale_want):
+    """exp() differs in the last bits between the host and the device, so a value that lands on a rounding
+    boundary may move by one step: scales to 1e-5 relative, values within 1, at most 1 % of them different."""
+    assert torch.allclose(scale_got.cpu(), scale_want, rtol=1e-5, atol=1e-12)
+    d = (got.cpu().to(torch.int16) - want.to(torch.int16)).abs()
+    assert int(d.max()) <= 1 and float((d > 0).float().mean()) <= 0.01
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape,smooth,left", [((3, 17, 512), "x", True), ((64, 16384), "f32", True),
+                                               ((9, 57344), None, True), ((33, 2048 + 64), "x", False),
+                                               ((4, 16), None, False), ((2, 65536), "f32", True)])
+def test_swiglu_quant_matches_oracle(pb, dtype, shape, smooth, left):
+    g = torch.Generator().manual_seed(shape[-1])
+    x = (torch.randn(shape, generator=g) * 1.5).to(dtype)
+    f = shape[-1] // 2
+    sm = None
+    if smooth is not None:
+        sm = (torch.rand(f, generator=g) * 1.5 + 0.5).to(dtype if smooth == "x" else torch.float32)
+    y, s = pb.npu_swiglu_quant(x.cuda(), smooth_scales=None if sm is None else sm.cuda(), activate_left=left,
+                               quant_mode=1)
+    yo, so = oracle.swiglu_quant(x, sm, activate_left=left)
+    assert y.shape == (*shape[:-1], f) and y.dtype == torch.int8 and s.shape == shape[:-1]
+    close_int8(y, yo, s, so)
+
+
+def test_swiglu_quant_rejects_unsupported(pb):
+    x = torch.zeros((2, 64), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="quant_mode"):
+        pb.npu_swiglu_quant(x)                                        # the default is the static mode
+    with pytest.raises(RuntimeError, match="even"):
+        pb.npu_swiglu_quant(torch.zeros((2, 63), dtype=torch.bfloat16, device="cuda"), quant_mode=1)
+    with pytest.raises(RuntimeError, match="multiple of 8"):
+        pb.npu_swiglu_quant(torch.zeros((2, 20), dtype=torch.bfloat16, device="cuda"), quant_mode=1)
+    y, s = pb.npu_swiglu_quant(torch.zeros((0, 64), dtype=torch.bfloat16, device="cuda"), quant_mode=1)
+    assert y.shape == (0, 32) and s.shape == (0,)
+
+
+def test_w8a8_swiglu_mlp_matches_oracle_chain(pb):
+    from pytorch_b200.contrib.function import w8a8_swiglu_mlp
+    g = torch.Generator().manual_seed(21)
+    m, k, f, h = 48, 256, 384, 128
+    x = torch.randn((m, k), generator=g).to(torch.bfloat16)
+    sm_in = (torch.rand(k, generator=g) + 0.5)
+    sm_act = (torch.rand(f, generator=g) + 0.5)
+    w_gu = torch.randint(-127, 128, (2 * f, k), generator=g).to(torch.int8)
+    w_dn = torch.randint(-127, 128, (h, f), generator=g).to(torch.int8)
+    s_gu = torch.rand(2 * f, generator=g) * 2e-3 + 1e-3
+    s_dn = torch.rand(h, generator=g) * 2e-3 + 1e-3
+    got = w8a8_swiglu_mlp(x.cuda(), sm_in.cuda(), w_gu.cuda(), s_gu.cuda(), sm_act.cuda(), w_dn.cuda(), s_dn.cuda())
+    q, s = oracle.dynamic_quant(x, sm_in)
+    gu = oracle.quant_matmul(q, w_gu.t(), s_gu, pertoken_scale=s, output_dtype=torch.bfloat16)
+    qa, sa = oracle.swiglu_quant(gu, sm_act, activate_left=True)
+    want = oracle.quant_matmul(qa, w_dn.t(), s_dn, pertoken_scale=sa, output_dtype=torch.bfloat16)
+    assert got.shape == (m, h) and got.dtype == torch.bfloat16
+    # int8 activations may differ by one step in a few places (see close_int8): bf16 output within 2^-6
+    assert oracle.max_mixed_error(got.cpu(), want) <= 2.0 ** -6

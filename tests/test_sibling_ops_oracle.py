@@ -68,3 +68,17 @@ def test_group_index_selects_the_smooth_row():
     y3, s3, o3 = oracle.dynamic_quant_asymmetric(x, sm, gi)
     y3b, s3b, o3b = oracle.dynamic_quant_asymmetric(x[4:], sm[2])
     assert torch.equal(y3[4:], y3b) and torch.equal(s3[4:], s3b) and torch.equal(o3[4:], o3b)
+
+
+def test_swiglu_quant_oracle_properties():
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn((5, 128), generator=g).to(torch.bfloat16)
+    sm = (torch.rand(64, generator=g) + 0.5).to(torch.bfloat16)
+    y, s = oracle.swiglu_quant(x, sm, activate_left=True)
+    act = torch.nn.functional.silu(x[:, :64].float()) * x[:, 64:].float() * sm.float()
+    assert y.shape == (5, 64) and s.shape == (5,)
+    assert torch.allclose(s, act.abs().max(-1).values / 127, rtol=1e-5)
+    assert int((y.float() - torch.round(act / s[:, None])).abs().max()) <= 1
+    # the other half activated: same as swapping the halves
+    y2, s2 = oracle.swiglu_quant(torch.cat([x[:, 64:], x[:, :64]], -1), sm, activate_left=False)
+    assert torch.equal(y, y2) and torch.equal(s, s2)
