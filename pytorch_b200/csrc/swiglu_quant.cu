@@ -19,15 +19,16 @@ __device__ __forceinline__ float silu_mul(float a, float b) {
   return __fmul_rn(__fmul_rn(a, s), b);
 }
 
-template <typename T, typename ST, int ITERS>
-__global__ void __launch_bounds__(512)
+template <typename T, typename ST, int ITERS, bool WIDE>
+__global__ void __launch_bounds__(WIDE ? 1024 : 512)
 swiglu_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth, int8_t* __restrict__ y,
                   float* __restrict__ scale_out, int64_t rows, int f, int act_offset, int gate_offset) {
   __shared__ float red[2][32];
   const int nvec = f >> 3;
   // Rows up to 16384 outputs wide keep the next row's packed loads in flight during the arithmetic of
-  // the current one; wider rows need the registers for the fp32 activations and load as they go.
-  constexpr bool PREFETCH = ITERS <= 4;
+  // the current one.  Wider rows (WIDE: up to 1024 threads with four vectors each, 64 registers) need
+  // the registers for the fp32 activations and load as they go; the larger CTA hides the latency.
+  constexpr bool PREFETCH = !WIDE;
   uint4 ra[PREFETCH ? ITERS : 1], rb[PREFETCH ? ITERS : 1];
   // A thread's vector past the end of the row repeats the row's last vector (not stored).
   auto load_row = [&](int64_t row) {
@@ -91,26 +92,23 @@ int launch_swiglu_quant(const void* x, const void* smooth, int8_t* y, float* sca
   const int nvec = (int)(f / 8);
   int iters = 1;
   while (iters < 4 && nvec > iters * 256) iters *= 2;
-  if (nvec > 4 * 512)
-    while (iters < 8 && nvec > iters * 512) iters *= 2;
+  const bool wide = nvec > 4 * 512;                      // four vectors per thread, up to 1024 threads
   int threads = (int)ceil_div(nvec, iters);
   threads = (int)ceil_div(threads, 32) * 32;
   const int act_off = activate_left ? 0 : (int)f, gate_off = activate_left ? (int)f : 0;
   int per_sm = 1;
-#define B200Q_SGQ_CASE(I)                                                                                    \
-  case I: {                                                                                                  \
-    auto kern = swiglu_quant_rows<T, ST, I>;                                                                 \
+#define B200Q_SGQ_CASE(I, W)                                                                                 \
+  {                                                                                                          \
+    auto kern = swiglu_quant_rows<T, ST, I, W>;                                                              \
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0);                                \
     const int64_t cap = (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);                                     \
     kern<<<(unsigned)(rows < cap ? rows : cap), threads, 0, st>>>(xp, sp, y, scale, rows, (int)f, act_off,   \
                                                                   gate_off);                                 \
-  } break;
-  switch (iters) {
-    B200Q_SGQ_CASE(1)
-    B200Q_SGQ_CASE(2)
-    B200Q_SGQ_CASE(4)
-    B200Q_SGQ_CASE(8)
   }
+  if (wide) B200Q_SGQ_CASE(4, true)
+  else if (iters == 1) B200Q_SGQ_CASE(1, false)
+  else if (iters == 2) B200Q_SGQ_CASE(2, false)
+  else B200Q_SGQ_CASE(4, false)
 #undef B200Q_SGQ_CASE
   return check_launch("swiglu_quant");
 }
@@ -134,7 +132,7 @@ extern "C" int b200q_swiglu_quant(const void* x, int x_dtype, const void* smooth
     return e == cudaSuccess ? B200Q_OK : fail(B200Q_ERR_LAUNCH, "swiglu_quant: %s", cudaGetErrorString(e));
   }
   B200Q_REQUIRE(x != nullptr && y != nullptr, B200Q_ERR_BAD_ARG, "swiglu_quant: x or y is NULL");
-  B200Q_REQUIRE(f % 8 == 0 && f <= 8 * 512 * 8, B200Q_ERR_UNSUPPORTED,
+  B200Q_REQUIRE(f % 8 == 0 && f <= 8 * 1024 * 4, B200Q_ERR_UNSUPPORTED,
                 "swiglu_quant: the output width (%lld) must be a multiple of 8 and at most 32768", (long long)f);
   B200Q_REQUIRE(aligned(x, 16) && aligned(y, 8) && aligned(scale, 4) && (smooth == nullptr || aligned(smooth, 16)),
                 B200Q_ERR_BAD_ARG, "swiglu_quant: x and smooth_scales must be 16-byte aligned, y 8-byte aligned");

@@ -84,6 +84,20 @@ def bench_dq_asym(m, k, iters, plain):
             "gbs": round(by / ms / 1e6, 1), "algorithmic_bytes": by}
 
 
+def bench_swiglu_quant(m, f, iters, plain):
+    lib = cabi.lib()
+    xs = [torch.randn(m, 2 * f, device="cuda", dtype=torch.bfloat16) for _ in range(min(_copies(m * f * 5), 64))]
+    sm = torch.rand(f, device="cuda") + 0.5
+    y = torch.empty(m, f, device="cuda", dtype=torch.int8)
+    s = torch.empty(m, device="cuda")
+    calls = [(lambda sp, x=x: cabi.check(lib.b200q_swiglu_quant(x.data_ptr(), cabi.BF16, sm.data_ptr(), cabi.F32, 1,
+                                                                y.data_ptr(), s.data_ptr(), m, f, sp))) for x in xs]
+    ms = _graph_time(calls, iters, plain)
+    by = 4 * m * f + m * f + 4 * m + 4 * f
+    return {"op": "swiglu_quant", "m": m, "f": f, "us": round(ms * 1e3, 2), "gbs": round(by / ms / 1e6, 1),
+            "algorithmic_bytes": by}
+
+
 def bench_anti_quant(m, n, bits, iters, plain):
     lib = cabi.lib()
     in_bytes = m * n * bits // 8
@@ -156,7 +170,7 @@ def bench_w4(m, k, n, gs, iters, plain):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["dq", "dqa", "aq", "qmm", "w4", "suite"])
+    ap.add_argument("op", choices=["dq", "dqa", "sgq", "aq", "qmm", "w4", "suite"])
     ap.add_argument("--bits", type=int, default=8)
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--k", type=int, default=4096)
@@ -171,6 +185,8 @@ def main():
         print(json.dumps(bench_dq(a.m, a.k, a.iters, a.plain)))
     elif a.op == "dqa":
         print(json.dumps(bench_dq_asym(a.m, a.k, a.iters, a.plain)))
+    elif a.op == "sgq":
+        print(json.dumps(bench_swiglu_quant(a.m, a.n, a.iters, a.plain)))
     elif a.op == "aq":
         print(json.dumps(bench_anti_quant(a.m, a.n, a.bits, a.iters, a.plain)))
     elif a.op == "qmm":
@@ -186,6 +202,7 @@ def main():
         for m in workloads.C3_M:
             print(json.dumps(bench_w4(m, workloads.C3_K, workloads.C3_N, workloads.C3_GS, a.iters, a.plain)), flush=True)
         print(json.dumps(bench_dq_asym(4096, 8192, a.iters, a.plain)), flush=True)
+        print(json.dumps(bench_swiglu_quant(4096, 28672, a.iters, a.plain)), flush=True)
         for bits in (8, 4):
             print(json.dumps(bench_anti_quant(8192, 8192, bits, a.iters, a.plain)), flush=True)
         print(json.dumps({"device_error": cabi.device_error()}))
