@@ -430,6 +430,8 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS to 1 for its children; the CPU arm uses every host core.
+    torch.set_num_threads(os.cpu_count() or 1)
     from oracle import quant_oracle as oracle
     rows = 128
     g = torch.Generator().manual_seed(5000)
