@@ -6,7 +6,7 @@ from hypothesis import given, settings, strategies as st
 
 from oracle import quant_oracle as oracle
 
-SETTINGS = dict(max_examples=25, deadline=None)
+SETTINGS = dict(max_examples=25, deadline=None, derandomize=True)   # same examples on every run
 
 
 def rand(shape, seed, dtype=torch.bfloat16, scale=1.0):
