@@ -50,6 +50,21 @@ const char* b200q_status_string(int status);
  * 0 means no kernel gave up a bounded wait.  Synchronises the device. */
 int b200q_device_error(unsigned int* code, int reset);
 
+/* Optional mirror of the error word in mapped pinned host memory.  After b200q_enable_host_error_word()
+ * (once per device, with that device current; it allocates one pinned host word and synchronises), a
+ * kernel that records an error also writes the code to the mirror, and b200q_peek_device_error() reads
+ * it without touching the device: a host layer can check it at every call for free.  0 = no error.
+ * The same role as the reference's asynchronous error surfacing at the next call
+ * (torch_npu/csrc/framework/OpParamMaker.cpp:258-264). */
+int b200q_enable_host_error_word(void);
+unsigned int b200q_peek_device_error(void);
+
+/* Self-test of the bounded waits: launches one warp that waits on a barrier nothing will ever arrive on,
+ * with a budget of limit_ns (1 ns .. 1 s).  The kernel returns by itself; afterwards b200q_device_error
+ * reports code 0x1FF.  Nothing faults or traps.  Counterpart of the reference's watchdog test, which
+ * lets a collective time out on purpose (test/distributed/test_watchdog.py:15-32). */
+int b200q_selftest_expire_wait(uint64_t limit_ns, void* stream);
+
 /* npu_dynamic_quant(input, smooth_scales=None) -> (int8 y, fp32 scale)
  *   replaces op_plugin::npu_dynamic_quant / aclnn DynamicQuant, reached from
  *   torch_npu/onnx/wrapper_onnx_ops.py:743-745; output contract test/test_fake_tensor.py:1671-1686.
@@ -103,11 +118,27 @@ typedef struct {
                               after the scales                                                */
   int bias_dtype;
   void* out;               /* [m,n], row stride out_row_stride (n when that field is 0)       */
-  int out_dtype;           /* B200Q_I8, B200Q_F16, B200Q_BF16 or B200Q_I32                    */
+  int out_dtype;           /* B200Q_I8, B200Q_F16, B200Q_BF16, B200Q_I32 (accumulator) or
+                              B200Q_F32 (dequantised value before the output cast)            */
   void* workspace;         /* >= b200q_quant_matmul_workspace_bytes(), 256-byte aligned       */
   size_t workspace_bytes;
   int64_t out_row_stride;  /* elements between rows of out; 0 means n.  A larger stride lets a
                               column shard be written straight into its place in an [m, N] matrix */
+  /* Multi-GPU epilogues: the GEMM itself stores finished tiles into peers' memory (peer-mapped device
+   * pointers, plain 128-bit stores over NVLink, full 128-byte lines), so the exchange overlaps the main
+   * loop tile by tile.  They take the place of the collective that follows the matmul in the reference:
+   * hcclAllGather of a column-sharded output (torch_npu/csrc/distributed/ProcessGroupHCCL.cpp:5896-5956) and
+   * the reduce-scatter inside npu_mm_reduce_scatter_base (torch_npu/distributed/tensor/_matrix_ops.py:556-561).
+   *   replicate (route_rows == 0, n_peer_out = 1..8): every element written to out[...] is also written to
+   *     the same offset from peer_out[i], the address of the same block in peer i's matrix.
+   *   routed (route_rows > 0): row r goes to row r % route_rows of peer_out[r / route_rows]
+   *     (ceil(m / route_rows) <= 8 entries, one of which may be local memory; row stride out_row_stride);
+   *     `out` is ignored.  With out_dtype B200Q_F32 this is the scatter half of a reduce-scatter.
+   * Needs out_dtype bf16/f16/f32/i32, n*size a multiple of 128 bytes, 16-byte aligned destinations and
+   * operands that meet the TMA rules; the caller orders a cross-rank barrier after the call. */
+  void* const* peer_out;   /* HOST array of device pointers, or NULL                                   */
+  int n_peer_out;
+  int64_t route_rows;
 } b200q_quant_matmul_args;
 
 size_t b200q_quant_matmul_workspace_bytes(int64_t m, int64_t k, int64_t n, int64_t x2_stride_k,
@@ -184,6 +215,23 @@ int b200q_anti_quant(const void* x, int src_bits, const void* scale, const void*
  *   (torch_npu/csrc/distributed/ProcessGroupHCCL.cpp:5896-5956) for this path. */
 int b200q_scatter_columns(const void* src, void* const* peer_dst, int n_peers, int64_t rows,
                           int64_t row_stride_bytes, int64_t col_offset_bytes, int64_t block_bytes, void* stream);
+
+/* Cross-rank barrier for the multi-GPU epilogues above: `flags` is a HOST array of `world` device
+ * pointers, flags[i] = rank i's array of `world` zero-initialised uint32 words, mapped for peer access.
+ * Rank `rank` announces `epoch` (1, 2, 3 ... the same on every rank for the same barrier) to every peer
+ * and waits until every peer has announced it; everything the stream wrote before (pushes included) is
+ * ordered before the announcement.  The wait is bounded by timeout_ns (0 = 10 s): when a peer does not
+ * arrive the kernel records code 0x104 in the device error word and returns, it never traps.
+ *   replaces the synchronisation inside hcclAllGather / HcclReduceScatter for this path. */
+int b200q_peer_barrier(void* const* flags, int world, int rank, uint32_t epoch, uint64_t timeout_ns, void* stream);
+
+/* Reduce half of npu_mm_reduce_scatter_base / npu_mm_all_reduce_base (golden:
+ * test/distributed/tensor/test_matrix_ops.py:86-110, partial products added in rank order in fp32):
+ * out[r,c] = cast(slots[0][r][c] + slots[1][r][c] + ... ), slots f32 [n_slots, rows, n] contiguous, out
+ * [rows, n] bf16/f16/f32; the result is also stored at the same offset of each peer_out[i] (HOST array of
+ * n_peer_out device pointers into peers' memory, or NULL/0).  rows*n must be a multiple of 4. */
+int b200q_reduce_slots(const float* slots, int n_slots, int64_t rows, int64_t n, void* out, int out_dtype,
+                       void* const* peer_out, int n_peer_out, void* stream);
 
 /* npu_trans_quant_param(scale, offset=None): fp32 scale -> int64 dequant parameter
  *   (torch_npu/contrib/module/linear_quant.py:107-108; contract test/test_fake_tensor.py:1929-1943).

@@ -196,6 +196,64 @@ def quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None,
     return _cast_out(v, out_dtype)
 
 
+# --------------------------------------------------------------- collective-fused forms
+def mm_reduce_scatter(x1_list, x2_list, x1_scale_list=None, x2_scale_list=None, bias_list=None,
+                      output_dtype=torch.bfloat16):
+    """``npu_mm_reduce_scatter_base`` (int8 form) for every rank at once: rank i holds ``x1_list[i]``
+    ``[m, k_i]`` and ``x2_list[i]`` ``[k_i, n]``; returns the list of per-rank outputs ``[m/g, n]``.
+
+    Follows ``TestMmReduceScatterBaseOp._get_global_tensor``
+    (``test/distributed/tensor/test_matrix_ops.py:86-110``): each rank's product (+ its int32 bias) is
+    dequantised with its own ``x1_scale [m,1]`` and ``x2_scale [1,n]``, the fp32 partials are added in rank
+    order starting from zero, and the sum is cast once.  The dequantisation of one partial is
+    ``quant_matmul`` above, i.e. ``(float(acc) * x2_scale[n]) * x1_scale[m]``; the golden multiplies the two
+    scales first, which differs by fp32 rounding only (checked against the golden in the tests)."""
+    g = len(x1_list)
+    total = None
+    for i in range(g):
+        n = x2_list[i].shape[1]
+        sc = x2_scale_list[i].reshape(-1) if x2_scale_list is not None else torch.ones(1)
+        pt = x1_scale_list[i].reshape(-1) if x1_scale_list is not None else None
+        part = quant_matmul(x1_list[i], x2_list[i], sc, pertoken_scale=pt,
+                            bias=None if bias_list is None else bias_list[i], output_dtype=torch.float32).numpy()
+        total = part.astype(F32) if total is None else (total + part).astype(F32)
+    m = total.shape[0]
+    if m % g:
+        raise ValueError(f"m={m} is not divisible by the number of ranks {g}")
+    out = _cast_out(total, output_dtype)
+    return [out[r * (m // g):(r + 1) * (m // g)] for r in range(g)]
+
+
+def mm_all_reduce(x1_list, x2_list, dequant_scale, pertoken_scale=None, output_dtype=None):
+    """``npu_mm_all_reduce_base`` (int8 form): the rank-ordered fp32 sum of the dequantised partial
+    products, the same ``[m, n]`` on every rank.  Output type: bf16 for a bf16 ``dequant_scale``, else fp16
+    (``test/test_fake_tensor.py:1555-1583``)."""
+    if output_dtype is None:
+        output_dtype = torch.bfloat16 if dequant_scale.dtype == torch.bfloat16 else torch.float16
+    total = None
+    for x1, x2 in zip(x1_list, x2_list):
+        part = quant_matmul(x1, x2, dequant_scale, pertoken_scale=pertoken_scale, output_dtype=torch.float32).numpy()
+        total = part.astype(F32) if total is None else (total + part).astype(F32)
+    return _cast_out(total, output_dtype)
+
+
+def all_gather_mm(x1_list, x2_list, x1_scale_list=None, x2_scale_list=None, bias_list=None,
+                  output_dtype=torch.bfloat16):
+    """``npu_all_gather_base_mm`` (int8 form) for every rank at once: ``x1_list[i]`` ``[m_i, k]`` is
+    gathered along rows, rank i multiplies the gathered matrix by its ``x2_list[i]`` ``[k, n_i]``.  Returns
+    ``([out_i [m, n_i]], gathered x1)`` as ``TestAllGatherBaseMmOp._get_global_tensor`` defines them
+    (``test/distributed/tensor/test_matrix_ops.py:21-40``): bias joins the accumulator, then
+    ``x1_scale * x2_scale * acc``."""
+    x1 = torch.cat(list(x1_list), dim=0)
+    pt = torch.cat([s.reshape(-1) for s in x1_scale_list]) if x1_scale_list is not None else None
+    outs = []
+    for i, x2 in enumerate(x2_list):
+        sc = x2_scale_list[i].reshape(-1) if x2_scale_list is not None else torch.ones(1)
+        outs.append(quant_matmul(x1, x2, sc, pertoken_scale=pt, bias=None if bias_list is None else bias_list[i],
+                                 output_dtype=output_dtype))
+    return outs, x1
+
+
 def trans_quant_param(scale, offset=None):
     """``npu_trans_quant_param(scale, offset=None)`` -> int64 dequant parameter.
 

@@ -26,6 +26,9 @@ OPS = (
     "npu_dynamic_quant_asymmetric",
     "npu_anti_quant",
     "npu_swiglu_quant",
+    "npu_mm_reduce_scatter_base",
+    "npu_all_gather_base_mm",
+    "npu_mm_all_reduce_base",
 )
 
 
@@ -47,6 +50,12 @@ npu_trans_quant_param = _torch.ops.npu.npu_trans_quant_param
 npu_dynamic_quant_asymmetric = _torch.ops.npu.npu_dynamic_quant_asymmetric
 npu_anti_quant = _torch.ops.npu.npu_anti_quant
 npu_swiglu_quant = _torch.ops.npu.npu_swiglu_quant
+
+from . import collective_ops  # noqa: E402,F401  (defines the three collective-fused operators in torch.ops.npu)
+
+npu_mm_reduce_scatter_base = _torch.ops.npu.npu_mm_reduce_scatter_base
+npu_all_gather_base_mm = _torch.ops.npu.npu_all_gather_base_mm
+npu_mm_all_reduce_base = _torch.ops.npu.npu_mm_all_reduce_base
 
 from . import contrib  # noqa: E402,F401
 

@@ -26,7 +26,8 @@ EXPORTS = (
     "b200q_static_scratch_bytes", "b200q_quant_matmul_static_scratch",
     "b200q_weight_quant_matmul_workspace_bytes", "b200q_weight_quant_matmul", "b200q_int4pack",
     "b200q_trans_quant_param", "b200q_scatter_columns", "b200q_dynamic_quant_ext", "b200q_anti_quant",
-    "b200q_swiglu_quant",
+    "b200q_swiglu_quant", "b200q_enable_host_error_word", "b200q_peek_device_error", "b200q_selftest_expire_wait",
+    "b200q_peer_barrier", "b200q_reduce_slots",
 )
 
 
@@ -42,6 +43,7 @@ class QuantMatmulArgs(C.Structure):
         ("out", C.c_void_p), ("out_dtype", C.c_int),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("out_row_stride", C.c_int64),
+        ("peer_out", C.POINTER(C.c_void_p)), ("n_peer_out", C.c_int), ("route_rows", C.c_int64),
     ]
 
 
@@ -100,6 +102,11 @@ def lib() -> C.CDLL:
                                          C.c_int64, C.c_int64, C.c_void_p]
         l.b200q_anti_quant.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int,
                                        C.c_int64, C.c_int64, C.c_void_p]
+        l.b200q_peek_device_error.restype = C.c_uint
+        l.b200q_selftest_expire_wait.argtypes = [C.c_uint64, C.c_void_p]
+        l.b200q_peer_barrier.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_uint32, C.c_uint64, C.c_void_p]
+        l.b200q_reduce_slots.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_int,
+                                         C.POINTER(C.c_void_p), C.c_int, C.c_void_p]
         l.b200q_scatter_columns.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int64, C.c_int64, C.c_int64,
                                             C.c_int64, C.c_void_p]
         _lib = l
@@ -196,8 +203,12 @@ def anti_quant(x: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor | None
 
 def quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None, output_dtype=None,
                  workspace: torch.Tensor | None = None, out: torch.Tensor | None = None,
-                 static_scratch: bool = False):
+                 static_scratch: bool = False, peer_out=None, route_rows: int = 0, out_row_stride: int = 0):
     """2-D ``x2`` only (any strides); leading dimensions of ``x1`` are folded into m.
+
+    ``peer_out`` (device addresses) with ``route_rows == 0``: the epilogue also stores the block at each
+    of those addresses (the same block inside the peers' matrices).  With ``route_rows > 0`` row r goes to
+    row ``r % route_rows`` of ``peer_out[r // route_rows]`` and ``out`` is not written (returns None).
 
     ``static_scratch=True`` goes through ``b200q_quant_matmul_static_scratch``: no workspace is
     allocated or passed; the library's built-in scratch array is used instead (``out`` should then be
@@ -207,7 +218,7 @@ def quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None, 
     x1c = x1.contiguous()
     k, n = x2.shape
     m = x1c.numel() // k if k else int(torch.Size(x1c.shape[:-1]).numel())
-    if out is None:
+    if out is None and not route_rows:
         out = torch.empty((*x1c.shape[:-1], n), dtype=out_dtype, device=x1.device)
     need = lib().b200q_quant_matmul_workspace_bytes(m, k, n, x2.stride(0), x2.stride(1))
     if workspace is None and need and not static_scratch:
@@ -229,9 +240,15 @@ def quant_matmul(x1, x2, scale, *, offset=None, pertoken_scale=None, bias=None, 
     if bias is not None:
         b = bias.contiguous(); keep.append(b)
         a.bias, a.bias_dtype = b.data_ptr(), DTYPE.get(b.dtype, 99)
-    a.out, a.out_dtype = out.data_ptr(), DTYPE.get(out_dtype, 99)
-    if out.dim() >= 2 and out.stride(-1) == 1 and out.stride(-2) != n and m > 1:
+    a.out, a.out_dtype = (None if out is None else out.data_ptr()), DTYPE.get(out_dtype, 99)
+    if out is not None and out.dim() >= 2 and out.stride(-1) == 1 and out.stride(-2) != n and m > 1:
         a.out_row_stride = out.stride(-2)      # a column slice of a wider matrix
+    if out_row_stride:
+        a.out_row_stride = out_row_stride
+    if peer_out is not None:
+        arr = (C.c_void_p * max(len(peer_out), 1))(*[C.c_void_p(int(p)) for p in peer_out])
+        keep.append(arr)
+        a.peer_out, a.n_peer_out, a.route_rows = arr, len(peer_out), route_rows
     if static_scratch:
         check(lib().b200q_quant_matmul_static_scratch(C.byref(a), _stream()))
         return out
@@ -306,3 +323,26 @@ def scatter_columns(full: torch.Tensor, peer_ptrs, col_lo: int, col_hi: int) -> 
     arr = (C.c_void_p * max(len(peer_ptrs), 1))(*[C.c_void_p(int(p)) for p in peer_ptrs])
     check(lib().b200q_scatter_columns(_ptr(full), arr, len(peer_ptrs), full.shape[0], full.shape[1] * es,
                                       col_lo * es, (col_hi - col_lo) * es, _stream()))
+
+
+def reduce_slots(slots: torch.Tensor, out: torch.Tensor, peer_out=()) -> torch.Tensor:
+    """``b200q_reduce_slots``: ``out = cast(slots[0] + slots[1] + ...)`` (fp32 adds in slot order); the result
+    is also stored at the device addresses ``peer_out`` (the same rows in the peers' matrices)."""
+    _need_cuda(slots, out)
+    if slots.dtype != torch.float32 or not slots.is_contiguous() or not out.is_contiguous():
+        raise B200QError(ERR_BAD_ARG, "reduce_slots: contiguous fp32 slots and a contiguous output are required")
+    n_slots, rows, n = slots.shape
+    arr = (C.c_void_p * max(len(peer_out), 1))(*[C.c_void_p(int(p)) for p in peer_out])
+    check(lib().b200q_reduce_slots(_ptr(slots), n_slots, rows, n, _ptr(out), DTYPE.get(out.dtype, 99), arr,
+                                   len(peer_out), _stream()))
+    return out
+
+
+def peer_barrier(flag_ptrs, rank: int, epoch: int, timeout_ns: int = 0) -> None:
+    """``b200q_peer_barrier`` over the flag arrays at the device addresses ``flag_ptrs`` (one per rank)."""
+    arr = (C.c_void_p * len(flag_ptrs))(*[C.c_void_p(int(p)) for p in flag_ptrs])
+    check(lib().b200q_peer_barrier(arr, len(flag_ptrs), rank, epoch & 0xFFFFFFFF, timeout_ns, _stream()))
+
+
+def selftest_expire_wait(limit_ns: int) -> None:
+    check(lib().b200q_selftest_expire_wait(limit_ns, _stream()))

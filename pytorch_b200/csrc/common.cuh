@@ -5,6 +5,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "../../include/b200q.h"
 
 namespace b200q {
@@ -31,5 +33,21 @@ inline int check_launch(const char* what) {
 }
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Raises the dynamic shared-memory limit of kernel `Kern` to `bytes`, once per device.  The per-device
+// record is guarded by a mutex, so concurrent first calls from several host threads are safe.
+template <auto Kern>
+int ensure_dynamic_smem(int bytes, const char* what) {
+  static std::mutex mu;
+  static bool done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = -1;
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev >= 0 && done[dev]) return B200Q_OK;
+  cudaError_t err = cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (err != cudaSuccess) return fail(B200Q_ERR_LAUNCH, "%s: cudaFuncSetAttribute: %s", what, cudaGetErrorString(err));
+  if (dev >= 0) done[dev] = true;
+  return B200Q_OK;
+}
 
 }  // namespace b200q

@@ -64,25 +64,34 @@ __device__ __forceinline__ void load_smooth8(const ST* p, float (&s)[8]) {
   }
 }
 
+// Reciprocal of a row's scale for quantize8.  0 for an all-zero row (every product is then 0); NaN marks
+// a scale so small that its reciprocal overflows or the refinement's residual could underflow: such a
+// row is quantised with true divisions instead (the same decision for every thread of the row).
+__device__ __forceinline__ float quant_inverse(float scale) {
+  if (scale == 0.0f) return 0.0f;
+  if (scale < 1e-30f) return __int_as_float(0x7fc00000);
+  return __frcp_rn(scale);
+}
+
 // Eight values -> eight int8 (packed), bit-exact with clamp(rint(xs / scale)).
-// Fast path: fma(xs, 1/scale, 1.5 * 2^23) rounds the product to the nearest-even integer and leaves
-// its two's-complement low byte in the low mantissa byte (|xs/scale| <= 127.0001 because
-// scale = amax/127, so no clamp is needed).  The product can differ from the IEEE quotient by at most
-// 1.2e-5 (127 * 2^-24 from the reciprocal, 2^-18 from the quotient's own rounding), so the two can
-// only round differently when it lies within that distance of a half-integer: a vector with a value
-// within 1e-4 of one is redone with IEEE division (about one warp instruction in twenty).
+// With y = RN(1/scale): q0 = RN(f*y) is within one ulp of the quotient, r = f - q0*scale is exact in one
+// fused multiply-add, and RN(q0 + r*y) is then the correctly rounded IEEE quotient (Markstein's division
+// refinement; it needs y correctly rounded, which __frcp_rn gives, and no overflow or underflow, which
+// quant_inverse rules out).  Adding 1.5 * 2^23 rounds that quotient to the nearest-even integer and leaves its
+// two's-complement low byte in the low mantissa byte; |xs/scale| <= 127.0001 because scale = amax/127,
+// so no clamp is needed.  No branch, no division.
 __device__ __forceinline__ uint2 quantize8(const float (&f)[8], float scale, float inv) {
   constexpr float kMagic = 12582912.0f;
   uint32_t u[8];
-  float dist = 0.0f;                                   // largest distance of a product from its rounded value
+  if (inv == inv) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float uf = __fmaf_rn(f[j], inv, kMagic);
-    const float t = __fsub_rn(uf, kMagic);
-    dist = fmaxf(dist, fabsf(__fmaf_rn(f[j], inv, -t)));
-    u[j] = __float_as_uint(uf);
-  }
-  if (dist > 0.4999f) {
+    for (int j = 0; j < 8; ++j) {
+      const float q0 = __fmul_rn(f[j], inv);
+      const float r = __fmaf_rn(-q0, scale, f[j]);
+      const float q = __fmaf_rn(r, inv, q0);
+      u[j] = __float_as_uint(__fadd_rn(q, kMagic));
+    }
+  } else {
 #pragma unroll
     for (int j = 0; j < 8; ++j) u[j] = (uint32_t)__float2int_rn(__fdiv_rn(f[j], scale));
   }
@@ -146,12 +155,105 @@ __global__ void __launch_bounds__(ITERS == 4 ? 1024 : 512) dynamic_quant_rows(co
     amax = block_max(amax, red[par]);
     const float scale = __fdiv_rn(amax, 127.0f);
     if (threadIdx.x == 0) scale_out[row] = scale;
-    const float inv = (scale == 0.0f) ? 0.0f : __frcp_rn(scale);   // all-zero row: every product is 0
+    const float inv = quant_inverse(scale);
     uint2* yr = reinterpret_cast<uint2*>(y + row * k) + threadIdx.x;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i)
       if (FULL || threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8(f[i], scale, inv));
   }
+}
+
+// Staged kernel.  Persistent CTAs stride over the rows; thread 0 keeps `stages` rows in flight with one
+// bulk copy per row into a shared-memory ring, each completing on its own mbarrier.  Per row: wait for the
+// row, pull this thread's ITERS vectors out of shared memory, form the fp32 products x*smooth once and
+// keep them in registers, reduce the row maximum (the __syncthreads inside also tells thread 0 that every
+// thread has finished reading the stage, so it refills it with the row `stages` ahead at once), quantise
+// from registers, stream the int8 out.  x is read from HBM exactly once and never waits on registers.
+template <typename T, typename ST, int ITERS, bool SMOOTH>
+__global__ void __launch_bounds__(512) dynamic_quant_staged(const T* __restrict__ x, const ST* __restrict__ smooth,
+                                                           int8_t* __restrict__ y, float* __restrict__ scale_out,
+                                                           int64_t rows, int k, int stages) {
+  extern __shared__ __align__(128) uint8_t dq_smem[];
+  __shared__ float red[2][32];
+  __shared__ uint64_t full[12];
+  __shared__ int abort_flag;
+  const int nvec = k >> 3;
+  const uint32_t row_bytes = (uint32_t)k * 2u;
+  const uint32_t ring = smem_u32(dq_smem);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < stages; ++i) mbar_init(&full[i], 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const uint64_t pol = policy_evict_first();
+  auto fetch = [&](int64_t row, int stage) {          // thread 0 only
+    mbar_arrive_expect_tx(&full[stage], row_bytes);
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(ring + (uint32_t)stage * row_bytes), "l"(x + row * k), "r"(row_bytes), "r"(smem_u32(&full[stage])), "l"(pol)
+        : "memory");
+  };
+  if (threadIdx.x == 0) {
+    int64_t r = blockIdx.x;
+    for (int i = 0; i < stages && r < rows; ++i, r += gridDim.x) fetch(r, i);
+  }
+  // The smooth scales of this thread's columns are the same for every row: keep them in registers when
+  // they fit (ITERS <= 2), else re-read them (they stay in L1).
+  float smk[ITERS <= 2 ? ITERS : 1][8];
+  if (SMOOTH && ITERS <= 2) {
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) load_smooth8(smooth + v * 8, smk[i]);
+    }
+  }
+  int stage = 0, par = 0;
+  uint32_t phase = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, par ^= 1) {
+    // A wait that gives up must end the loop for the whole CTA at the same place: the thread contributes a
+    // sentinel above every float to the maximum reduction below, which every thread then sees.
+    const bool got = mbar_wait(&full[stage], phase, &abort_flag, kDevTimeoutProducer);
+    const uint32_t src = ring + (uint32_t)stage * row_bytes + threadIdx.x * 16;
+    float f[ITERS][8];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      const bool in = got && v < nvec;
+      const uint4 raw = in ? ld_shared_v4(src + i * blockDim.x * 16) : make_uint4(0, 0, 0, 0);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      float sm[8];
+      if (SMOOTH && ITERS > 2 && in) load_smooth8(smooth + v * 8, sm);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 pr = unpack2<T>(w[j]);
+        const float s0 = !SMOOTH ? 1.0f : (ITERS <= 2 ? smk[ITERS <= 2 ? i : 0][2 * j] : sm[2 * j]);
+        const float s1 = !SMOOTH ? 1.0f : (ITERS <= 2 ? smk[ITERS <= 2 ? i : 0][2 * j + 1] : sm[2 * j + 1]);
+        f[i][2 * j] = (SMOOTH && in) ? __fmul_rn(pr.x, s0) : pr.x;
+        f[i][2 * j + 1] = (SMOOTH && in) ? __fmul_rn(pr.y, s1) : pr.y;
+        amax = fmaxf(amax, fmaxf(fabsf(f[i][2 * j]), fabsf(f[i][2 * j + 1])));
+      }
+    }
+    amax = block_max(got ? amax : __uint_as_float(0xFFFFFFFFu), red[par]);   // every thread has read its part of the stage
+    if (__float_as_uint(amax) == 0xFFFFFFFFu) break;
+    if (threadIdx.x == 0) {
+      const int64_t nxt = row + (int64_t)stages * gridDim.x;
+      if (nxt < rows) fetch(nxt, stage);
+    }
+    const float scale = __fdiv_rn(amax, 127.0f);
+    if (threadIdx.x == 0) scale_out[row] = scale;
+    const float inv = quant_inverse(scale);
+    uint2* yr = reinterpret_cast<uint2*>(y + row * k) + threadIdx.x;
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i)
+      if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8(f[i], scale, inv));
+    if (++stage == stages) { stage = 0; phase ^= 1; }
+  }
+  // Copies still in flight when a wait gave up must land before the shared memory is released.
+  if (abort_flag && threadIdx.x == 0)
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  __syncthreads();
 }
 
 // Generic path: any k, any alignment; the row is read twice (second pass from L2).
@@ -191,6 +293,36 @@ int launch_dq(const void* x, const void* smooth, int8_t* y, float* scale, int64_
     return check_launch("dynamic_quant (generic)");
   }
   const int nvec = (int)(k / 8);
+  if (k >= 1024 && k <= 32768) {
+    // Staged kernel: the fewest vectors per thread that keep the CTA at 384 threads or fewer (eight vectors
+    // and up to 512 threads for the longest rows); as many CTAs per SM as 64 KB (rows up to 16 KB), 96 KB
+    // (up to 32 KB) or 200 KB rings allow.
+    int it = 1;
+    while (it < 8 && ceil_div(nvec, it) > (it == 4 ? 512 : 384)) it *= 2;
+    int threads = (int)ceil_div(ceil_div(nvec, it), 32) * 32;
+    const int64_t row_bytes = k * 2;
+    const int64_t budget = row_bytes <= 16384 ? 65536 : row_bytes <= 32768 ? 98304 : 204800;
+    int stages = (int)(budget / row_bytes);
+    stages = stages > 12 ? 12 : stages < 2 ? 2 : stages;
+    const int smem = (int)(stages * row_bytes);
+    int per_sm = 1;
+#define B200Q_DQS_LAUNCH(I)                                                                                    \
+  {                                                                                                            \
+    constexpr auto kern = dynamic_quant_staged<T, ST, I, SMOOTH>;                                             \
+    if (int rc = ensure_dynamic_smem<kern>(204800, "dynamic_quant")) return rc;                               \
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem);                               \
+    const int64_t cap = (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);                                       \
+    kern<<<(unsigned)(rows < cap ? rows : cap), threads, smem, st>>>(xp, sp, y, scale, rows, (int)k, stages); \
+  }
+    switch (it) {
+      case 1: B200Q_DQS_LAUNCH(1) break;
+      case 2: B200Q_DQS_LAUNCH(2) break;
+      case 4: B200Q_DQS_LAUNCH(4) break;
+      default: B200Q_DQS_LAUNCH(8) break;
+    }
+#undef B200Q_DQS_LAUNCH
+    return check_launch("dynamic_quant (staged)");
+  }
   // Up to four 128-bit loads per thread (32 fp32 products kept in registers) with <= 256 threads where
   // the row allows it (k <= 8192); longer rows widen the CTA up to 1024 threads (k <= 32768), then take
   // 8 and 16 loads per thread with 512 threads.

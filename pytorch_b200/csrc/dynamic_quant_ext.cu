@@ -62,7 +62,7 @@ __device__ __forceinline__ uint2 quantize8_asym(const float (&f)[8], float scale
     dist = fmaxf(dist, fabsf(__fsub_rn(t, __fsub_rn(uf, kMagic))));
     u[j] = __float_as_uint(uf);
   }
-  if (dist > 0.4999f || scale == 0.0f) {
+  if (dist > 0.4999f || scale == 0.0f || !(inv < 3.0e38f)) {   // tiny scale: 1/scale overflowed
 #pragma unroll
     for (int j = 0; j < 8; ++j) u[j] = scale == 0.0f ? 0u : (uint32_t)quant_asym_exact(f[j], scale, offset);
   }
@@ -129,7 +129,7 @@ dynamic_quant_ext_rows(const T* __restrict__ x, const ST* __restrict__ smooth, c
       const float amax = fmaxf(fabsf(mx), fabsf(mn));
       const float scale = __fdiv_rn(amax, 127.0f);
       if (threadIdx.x == 0) scale_out[row] = scale;
-      const float inv = scale == 0.0f ? 0.0f : __frcp_rn(scale);
+      const float inv = quant_inverse(scale);
 #pragma unroll
       for (int i = 0; i < ITERS; ++i)
         if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8(f[i], scale, inv));

@@ -1,16 +1,22 @@
 // npu_convert_weight_to_int4pack and npu_trans_quant_param: small layout kernels.
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace b200q {
 namespace {
 
-// One thread packs eight int32-held int4 values (two 128-bit loads) into one int32.
-// Values are taken modulo 16, i.e. the two's-complement low nibble; value j of a group
-// lands in bits [4j, 4j+4).  Grid-stride over the output words.
+// One thread packs eight int32-held int4 values (two 128-bit loads) into one int32; value j of a
+// group lands in bits [4j, 4j+4).  Grid-stride over the output words.  A value outside [-8, 7] has no
+// int4 representation: its low nibble is packed, and the kernel records kDevInt4Range in the device
+// error word so that the caller learns about it (the CPU golden raises in the same situation).
 __global__ void int4pack_kernel(const int4* __restrict__ w, int32_t* __restrict__ packed, int64_t nwords) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nwords;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int4 a = __ldcs(w + 2 * i), b = __ldcs(w + 2 * i + 1);
+    // v in [-8, 7]  <=>  (v + 8) has no bit above bit 3
+    const uint32_t high = ((uint32_t)(a.x + 8) | (uint32_t)(a.y + 8) | (uint32_t)(a.z + 8) | (uint32_t)(a.w + 8) |
+                           (uint32_t)(b.x + 8) | (uint32_t)(b.y + 8) | (uint32_t)(b.z + 8) | (uint32_t)(b.w + 8)) & ~0xFu;
+    if (high) record_device_error(kDevInt4Range);
     const uint32_t v = (a.x & 0xF) | ((a.y & 0xF) << 4) | ((a.z & 0xF) << 8) | ((a.w & 0xF) << 12) |
                        ((b.x & 0xF) << 16) | ((b.y & 0xF) << 20) | ((b.z & 0xF) << 24) |
                        ((uint32_t)(b.w & 0xF) << 28);

@@ -10,15 +10,39 @@ namespace b200q {
 
 // Device-wide error word.  Kernels never trap or spin without bound: a wait that
 // exceeds its limit stores a code here and the kernel winds down.  The host reads
-// it with b200q_device_error().
+// it with b200q_device_error().  When the host has registered a mirror word in mapped
+// pinned host memory (b200q_enable_host_error_word), the first error is also stored there,
+// so that a host layer can notice it at its next call without synchronising the device.
 __device__ unsigned int g_device_error = 0;
+__device__ unsigned int* g_host_error_word = nullptr;
 
 enum DeviceErrorCode : unsigned int {
   kDevOk = 0,
   kDevTimeoutProducer = 0x101,   // TMA producer waited too long for a free stage
   kDevTimeoutMma = 0x102,        // MMA issuer waited too long for data / a free accumulator
   kDevTimeoutEpilogue = 0x103,   // epilogue waited too long for an accumulator
+  kDevTimeoutBarrier = 0x104,    // cross-rank barrier: a peer's flag did not arrive in time
+  kDevTimeoutSelfTest = 0x1FF,   // the wait self-test (b200q_selftest_expire_wait) ran out, as it should
+  kDevInt4Range = 0x201,         // npu_convert_weight_to_int4pack met a value outside [-8, 7]
 };
+
+// Records the first error of the device (later ones keep the first code).
+__device__ __forceinline__ void record_device_error(unsigned int code) {
+  if (atomicCAS(&g_device_error, 0u, code) == 0u) {
+    unsigned int* h = g_host_error_word;
+    if (h != nullptr) {
+      *reinterpret_cast<volatile unsigned int*>(h) = code;
+      __threadfence_system();
+    }
+  }
+}
+
+// Nanosecond wall clock of the GPU.  Unlike the SM cycle counter it does not depend on the SM clock.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -50,23 +74,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Cycle budget of one wait (~0.2 s at 1.9 GHz): far above any legitimate wait of
-// these kernels, small enough that a protocol error ends the launch quickly.
-constexpr long long kWaitLimitCycles = 400000000LL;
+// Time budget of one wait: 0.25 s, far above any legitimate wait of these kernels (the longest
+// kernel here runs about a millisecond), small enough that a protocol error ends the launch quickly.
+constexpr unsigned long long kWaitLimitNs = 250000000ULL;
 
 // Bounded wait.  Returns false when the CTA is aborting (another thread timed out)
 // or when this wait ran out of budget; in the second case it raises the abort flag
 // and records `code` in the device error word.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned int code) {
+                                          unsigned int code, unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
+  const unsigned long long t0 = global_timer_ns();
   for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int spin = 0; spin < 64; ++spin)
+      if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (global_timer_ns() - t0 > limit_ns) {
       *abort_flag = 1;
-      atomicCAS(&g_device_error, 0u, code);
+      record_device_error(code);
       return false;
     }
   }
@@ -256,6 +282,69 @@ __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc, ui
       "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// ------------------------------------------------- clusters: distributed shared memory
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t nclusters_x() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_acq_rel_cluster() {
+  asm volatile("fence.acq_rel.cluster;" ::: "memory");
+}
+// try_wait whose acquire covers writes released at cluster scope (a peer CTA's remote arrive).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  unsigned int code, unsigned long long limit_ns = kWaitLimitNs) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int spin = 0; spin < 64; ++spin)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > limit_ns) {
+      *abort_flag = 1;
+      record_device_error(code);
+      return false;
+    }
+  }
+}
+
+// 128-bit shared-memory accesses by 32-bit shared address.
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
 }
 
 // Named barrier among a subset of the CTA's warps (id 1..15; 0 is __syncthreads).

@@ -14,6 +14,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include <mutex>
+
 #include "b200q.h"
 
 namespace {
@@ -35,6 +37,24 @@ int dtype_enum(at::ScalarType t) {
 
 void check_status(int status, const char* op) {
   TORCH_CHECK(status == B200Q_OK, op, ": ", b200q_last_error(), " (", b200q_status_string(status), ")");
+}
+
+// A kernel that gives up a bounded wait returns early and leaves its output unfinished.  The library mirrors
+// the device's error word into pinned host memory, so every operator call can look at it for free and raise
+// (the error belongs to an earlier launch on this device; like the reference, which reports asynchronous
+// launch failures at the next call, torch_npu/csrc/framework/OpParamMaker.cpp:258-264).  The mirror is set up
+// on the first operator call on a device.
+void surface_device_error(const char* op, const Tensor& t) {
+  static std::once_flag once[64];
+  const int dev = t.device().index();
+  if (dev >= 0 && dev < 64) std::call_once(once[dev], [] { b200q_enable_host_error_word(); });
+  const unsigned int code = b200q_peek_device_error();
+  if (code != 0) {
+    unsigned int seen = 0;
+    b200q_device_error(&seen, 1);      // synchronises and clears, so that the next call can proceed
+    TORCH_CHECK(false, op, ": an earlier kernel on ", t.device(), " gave up a bounded wait (device error code 0x", std::hex,
+                code, "); its output is incomplete");
+  }
 }
 
 // Same rule and message as the reference's generated wrapper (torchnpugen/custom_functions.py:137-208;
@@ -87,6 +107,7 @@ std::tuple<Tensor, Tensor> dynamic_quant_cuda(const Tensor& input, const optiona
                                               optional<at::ScalarType> dst_type) {
   check_same_device("npu_dynamic_quant", input, {&smooth, &group_index});
   c10::cuda::CUDAGuard guard(input.device());
+  surface_device_error(__func__, input);
   auto [y, scale] = dynamic_quant_check(input, smooth, group_index, dst_type);
   Tensor x = input.contiguous();
   Tensor sm = smooth.has_value() ? smooth->contiguous() : Tensor();
@@ -115,6 +136,7 @@ std::tuple<Tensor, Tensor, Tensor> dynamic_quant_asym_cuda(const Tensor& input, 
                                                            optional<at::ScalarType> dst_type) {
   check_same_device("npu_dynamic_quant_asymmetric", input, {&smooth, &group_index});
   c10::cuda::CUDAGuard guard(input.device());
+  surface_device_error(__func__, input);
   auto [y, scale] = dynamic_quant_check(input, smooth, group_index, dst_type);
   Tensor offset = at::empty_like(scale);
   Tensor x = input.contiguous();
@@ -171,6 +193,7 @@ std::tuple<Tensor, Tensor> swiglu_quant_cuda(const Tensor& x, const optional<Ten
                                              optional<at::ScalarType> dst_type) {
   check_same_device("npu_swiglu_quant", x, {&smooth, &offsets, &group_index});
   c10::cuda::CUDAGuard guard(x.device());
+  surface_device_error(__func__, x);
   auto [y, scale] = swiglu_quant_check(x, smooth, offsets, group_index, quant_mode, dst_type);
   Tensor xc = x.contiguous();
   Tensor sm = smooth.has_value() ? smooth->contiguous() : Tensor();
@@ -221,6 +244,7 @@ Tensor anti_quant_cuda(const Tensor& x, const Tensor& scale, const optional<Tens
   TORCH_CHECK(scale.device() == x.device(), "Expected all tensors to be on the same device, but found at least two devices, ",
               x.device(), " and ", scale.device(), "! (npu_anti_quant)");
   c10::cuda::CUDAGuard guard(x.device());
+  surface_device_error(__func__, x);
   auto shape = anti_quant_check(x, scale, offset, dst_dtype, src_dtype);
   const at::ScalarType out_t = dst_dtype.value_or(at::kHalf);
   Tensor out = at::empty(shape, x.options().dtype(out_t));
@@ -286,7 +310,8 @@ QmmShape quant_matmul_check(const Tensor& x1, const Tensor& x2, const Tensor& sc
   }
   s.m_total = 1;
   for (size_t i = 0; i + 1 < s.out_shape.size(); ++i) s.m_total *= s.out_shape[i];
-  s.m_per_batch = x2.dim() == 3 ? x1.size(-2) : s.m_total;
+  // A 3-D x2 with a single batch is one weight for every row of x1: the batches of x1 fold into m.
+  s.m_per_batch = (x2.dim() == 3 && s.batch_x2 > 1) ? x1.size(-2) : s.m_total;
   if (pertoken.has_value()) {
     TORCH_CHECK(pertoken->scalar_type() == at::kFloat, "npu_quant_matmul: pertoken_scale should be torch.float32 datatype");
     TORCH_CHECK(pertoken->numel() == s.m_total || pertoken->numel() == 1, "npu_quant_matmul: pertoken_scale must have ",
@@ -309,6 +334,7 @@ Tensor quant_matmul_cuda(const Tensor& x1, const Tensor& x2, const Tensor& scale
   const optional<Tensor> x2o(x2), so(scale);
   check_same_device("npu_quant_matmul", x1, {&x2o, &so, &offset, &pertoken, &bias});
   c10::cuda::CUDAGuard guard(x1.device());
+  surface_device_error(__func__, x1);
   const at::ScalarType out_dtype = output_dtype.value_or(at::kChar);
   QmmShape s = quant_matmul_check(x1, x2, scale, offset, pertoken, bias, out_dtype);
   Tensor out = at::empty(s.out_shape, x1.options().dtype(out_dtype));
@@ -427,6 +453,7 @@ Tensor weight_quant_cuda(const Tensor& x, const Tensor& weight, const Tensor& sc
   const optional<Tensor> wo(weight), so(scale);
   check_same_device("npu_weight_quant_batchmatmul", x, {&wo, &so, &offset, &quant_scale, &quant_offset, &bias});
   c10::cuda::CUDAGuard guard(x.device());
+  surface_device_error(__func__, x);
   WqShape s = weight_quant_check(x, weight, scale, offset, quant_scale, quant_offset, bias, group_size, inner_precise,
                                  weight_dtype);
   Tensor out = at::empty(s.out_shape, x.options());
@@ -478,6 +505,7 @@ std::vector<int64_t> int4pack_shape(const Tensor& weight) {
 
 Tensor int4pack_cuda(const Tensor& weight, int64_t /*inner_k_tiles*/) {
   c10::cuda::CUDAGuard guard(weight.device());
+  surface_device_error(__func__, weight);
   Tensor out = at::empty(int4pack_shape(weight), weight.options());
   Tensor w = weight.contiguous();
   const int64_t cols = w.size(-1);
@@ -502,6 +530,7 @@ std::vector<int64_t> trans_shape(const Tensor& scale, const optional<Tensor>& of
 Tensor trans_quant_param_cuda(const Tensor& scale, const optional<Tensor>& offset) {
   check_same_device("npu_trans_quant_param", scale, {&offset});
   c10::cuda::CUDAGuard guard(scale.device());
+  surface_device_error(__func__, scale);
   Tensor out = at::empty(trans_shape(scale, offset), scale.options().dtype(at::kLong));
   Tensor sc = scale.contiguous();
   check_status(b200q_trans_quant_param(static_cast<const float*>(sc.data_ptr()), sc.numel(),

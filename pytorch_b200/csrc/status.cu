@@ -33,7 +33,51 @@ int sm_count() {
   return cached[dev];
 }
 
+// Mirror of the device error word in mapped pinned host memory, one per device, created on request.
+// Returns the host pointer of the current device's word (nullptr when there is none and `create` is false
+// or the mapping failed).
+unsigned int* host_error_word(bool create) {
+  static std::mutex mu;
+  static unsigned int* words[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (words[dev] == nullptr && create) {
+    unsigned int* h = nullptr;
+    unsigned int* d = nullptr;
+    if (cudaHostAlloc(reinterpret_cast<void**>(&h), sizeof(unsigned int), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer(reinterpret_cast<void**>(&d), h, 0) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    *h = 0;
+    if (cudaMemcpyToSymbol(g_host_error_word, &d, sizeof(d)) != cudaSuccess) {
+      cudaGetLastError();
+      cudaFreeHost(h);
+      return nullptr;
+    }
+    words[dev] = h;
+  }
+  return words[dev];
+}
+
+// Self-test of the bounded wait: one warp waits on an mbarrier that nothing will ever arrive on.  The wait must
+// run out after `limit_ns`, record kDevTimeoutSelfTest and let the kernel return normally.
+__global__ void expire_wait_kernel(unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, &abort_flag, kDevTimeoutSelfTest, limit_ns);
+  __syncthreads();
+}
+
 }  // namespace b200q
+
 
 extern "C" {
 
@@ -63,8 +107,29 @@ int b200q_device_error(unsigned int* code, int reset) {
     unsigned int z = 0;
     e = cudaMemcpyToSymbol(b200q::g_device_error, &z, sizeof(z));
     if (e != cudaSuccess) return b200q::fail(B200Q_ERR_LAUNCH, "b200q_device_error: %s", cudaGetErrorString(e));
+    if (unsigned int* h = b200q::host_error_word(false)) *reinterpret_cast<volatile unsigned int*>(h) = 0;
   }
   return v == 0 ? B200Q_OK : B200Q_ERR_DEVICE;
+}
+
+int b200q_enable_host_error_word(void) {
+  b200q::clear_error();
+  return b200q::host_error_word(true) != nullptr
+             ? B200Q_OK
+             : b200q::fail(B200Q_ERR_LAUNCH, "b200q_enable_host_error_word: could not map a pinned host word");
+}
+
+unsigned int b200q_peek_device_error(void) {
+  unsigned int* h = b200q::host_error_word(false);
+  return h ? *reinterpret_cast<volatile unsigned int*>(h) : 0u;
+}
+
+int b200q_selftest_expire_wait(uint64_t limit_ns, void* stream) {
+  b200q::clear_error();
+  B200Q_REQUIRE(limit_ns > 0 && limit_ns <= 1000000000ULL, B200Q_ERR_BAD_ARG,
+                "b200q_selftest_expire_wait: limit must be between 1 ns and 1 s");
+  b200q::expire_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns);
+  return b200q::check_launch("selftest_expire_wait");
 }
 
 }  // extern "C"

@@ -76,7 +76,7 @@ swiglu_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth, int8_t
     amax = block_max(amax, red[par]);
     const float scale = __fdiv_rn(amax, 127.0f);
     if (threadIdx.x == 0) scale_out[row] = scale;
-    const float inv = scale == 0.0f ? 0.0f : __frcp_rn(scale);
+    const float inv = quant_inverse(scale);
     uint2* yr = reinterpret_cast<uint2*>(y + row * f) + threadIdx.x;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i)

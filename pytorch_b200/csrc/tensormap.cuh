@@ -4,6 +4,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200q {
@@ -43,6 +45,43 @@ inline int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes
   CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(B200Q_ERR_LAUNCH, "%s: cuTensorMapEncodeTiled failed (CUresult %d)", what, (int)r);
+  return B200Q_OK;
+}
+
+// Same, through a small cache keyed by every argument: a weight is used with the same map call after
+// call, and encoding a map costs more than looking it up.  Thread-safe (one mutex); 256 direct-mapped
+// entries, a colliding key simply replaces the entry.
+inline int make_tmap_2d_cached(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const void* base,
+                               uint64_t inner, uint64_t outer, uint64_t pitch_bytes, uint32_t box_inner,
+                               uint32_t box_outer, CUtensorMapSwizzle swz, const char* what) {
+  struct Entry {
+    const void* base;
+    uint64_t inner, outer, pitch;
+    uint32_t box_inner, box_outer;
+    int dt, elem_bytes, swz;
+    bool valid;
+    CUtensorMap map;
+  };
+  static std::mutex mu;
+  static Entry table[256];
+  uint64_t h = reinterpret_cast<uint64_t>(base) * 0x9E3779B97F4A7C15ull;
+  h ^= (inner * 31 + outer) * 0xC2B2AE3D27D4EB4Full + pitch_bytes * 0x165667B19E3779F9ull + box_outer * 131 + box_inner;
+  Entry& e = table[(h >> 24) & 255];
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (e.valid && e.base == base && e.inner == inner && e.outer == outer && e.pitch == pitch_bytes &&
+        e.box_inner == box_inner && e.box_outer == box_outer && e.dt == (int)dt && e.elem_bytes == elem_bytes &&
+        e.swz == (int)swz) {
+      *out = e.map;
+      return B200Q_OK;
+    }
+  }
+  if (int rc = make_tmap_2d(out, dt, elem_bytes, base, inner, outer, pitch_bytes, box_inner, box_outer, swz, what)) return rc;
+  std::lock_guard<std::mutex> lock(mu);
+  e.base = base; e.inner = inner; e.outer = outer; e.pitch = pitch_bytes;
+  e.box_inner = box_inner; e.box_outer = box_outer; e.dt = (int)dt; e.elem_bytes = elem_bytes; e.swz = (int)swz;
+  e.map = *out;
+  e.valid = true;
   return B200Q_OK;
 }
 

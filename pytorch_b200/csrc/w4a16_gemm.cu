@@ -37,18 +37,6 @@
 namespace b200q {
 namespace {
 
-// Optional cycle accounting of the pipeline roles of CTA 0 (diagnostic builds only).
-#ifdef B200Q_DIAG_TIMING
-__device__ unsigned long long g_wq_diag[16];
-#define WQ_DIAG_BEGIN() long long diag_t0 = clock64()
-#define WQ_DIAG_ADD(var) do { long long diag_t1 = clock64(); (var) += diag_t1 - diag_t0; diag_t0 = diag_t1; } while (0)
-#define WQ_DIAG_STORE(idx, var) do { if (blockIdx.x == 0) g_wq_diag[idx] = (unsigned long long)(var); } while (0)
-#else
-#define WQ_DIAG_BEGIN() do {} while (0)
-#define WQ_DIAG_ADD(var) do {} while (0)
-#define WQ_DIAG_STORE(idx, var) do {} while (0)
-#endif
-
 constexpr int kWqBK = 64;                   // K elements per stage (one 128-byte swizzle row of bf16)
 constexpr int kWqTileN = 256;               // output channels per tile = UMMA N
 constexpr int kWqDeqWarps = 16;
@@ -387,9 +375,6 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      long long d_wait = 0, d_issue = 0;
-      (void)d_wait; (void)d_issue;
-      WQ_DIAG_BEGIN();
       WqWalk walk(p, blockIdx.x, gridDim.x);
       int unit, kb0, kb1;
       auto weight_coords = [&](int tn, int kb, int& c0, int& c1) {
@@ -402,9 +387,7 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           if (it % kWqProducers != warp) continue;
           const int stage = it % LS;
-          WQ_DIAG_ADD(d_issue);
           if (!mbar_wait(&done[stage], (uint32_t)((it / LS) & 1) ^ 1u, abort_flag, kDevTimeoutProducer)) { ok = false; break; }
-          WQ_DIAG_ADD(d_wait);
           mbar_arrive_expect_tx(&full[stage], C::kRawBytes + C::kXBytes);
           int c0, c1;
           weight_coords(tn, kb, c0, c1);
@@ -414,8 +397,6 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             tma_load_2d(sX + stage * C::kXBytes + ch * MM * 128, &tmX, &full[stage], kb * kWqBK, (mc * NCH + ch) * MM);
         }
       }
-      WQ_DIAG_STORE(0, d_wait);
-      WQ_DIAG_STORE(1, d_issue);
       if (!ok)
         for (int i = 0; i < 200; ++i) __nanosleep(1000);   // let copies in flight land before smem is released
     }
@@ -427,24 +408,15 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int it = 0;
       uint32_t tphase = 0;
       bool ok = true;
-      long long d_tempty = 0, d_aready = 0, d_issue = 0;
-      (void)d_tempty; (void)d_aready; (void)d_issue;
-      const long long d_start = clock64();
-      (void)d_start;
-      WQ_DIAG_BEGIN();
       WqWalk walk(p, blockIdx.x, gridDim.x);
       int unit, kb0, kb1;
       while (ok && walk.next(unit, kb0, kb1)) {
-        WQ_DIAG_ADD(d_issue);
         if (!mbar_wait(tempty, tphase ^ 1, abort_flag, kDevTimeoutMma)) { ok = false; break; }
-        WQ_DIAG_ADD(d_tempty);
         tc_fence_after();
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int stage = it % LS, slot = it % AS;
-          WQ_DIAG_ADD(d_issue);
           if (!mbar_wait(&aready[slot], (uint32_t)(it / AS) & 1u, abort_flag, kDevTimeoutMma) ||
               !mbar_wait(&full[stage], (uint32_t)(it / LS) & 1u, abort_flag, kDevTimeoutMma)) { ok = false; break; }
-          WQ_DIAG_ADD(d_aready);
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sX + stage * C::kXBytes), b_addr = smem_u32(sB + slot * kWqBBytes);
 #pragma unroll
@@ -465,12 +437,6 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         umma_commit(tfull);
         tphase ^= 1;
       }
-      WQ_DIAG_ADD(d_issue);
-      WQ_DIAG_STORE(2, d_tempty);
-      WQ_DIAG_STORE(3, d_aready);
-      WQ_DIAG_STORE(4, d_issue);
-      WQ_DIAG_STORE(5, clock64() - d_start);
-      WQ_DIAG_STORE(9, it);
     }
   } else {
     // ------------------------------------------- dequantise, then epilogue
@@ -485,9 +451,6 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     int it_base = 0;                                   // K blocks this CTA has been through before this segment
     uint32_t tphase = 0;
     bool ok = true;
-    long long d_wait = 0, d_work = 0, d_epi = 0;
-    (void)d_wait; (void)d_work; (void)d_epi;
-    WQ_DIAG_BEGIN();
     WqWalk walk(p, blockIdx.x, gridDim.x);
     int unit, kb0, kb1;
     while (ok && walk.next(unit, kb0, kb1)) {
@@ -515,13 +478,11 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           while (g_rem >= gs_blocks) { g_rem -= gs_blocks; ++g_next; }
           if (LAYOUT != kW8K && (int64_t)g_next != g) fetch_params8<XT>(p, g_next, n_oct0, ns, no);
         }
-        WQ_DIAG_ADD(d_work);
         // The tile must have landed, and the MMAs that read this operand slot AS tiles ago must have retired.
         bool got = mbar_wait(&full[stage], (uint32_t)(it / LS) & 1u, abort_flag, kDevTimeoutEpilogue);
         if (got && it >= AS)
           got = mbar_wait(&done[(it - AS) % LS], (uint32_t)((it - AS) / LS) & 1u, abort_flag, kDevTimeoutEpilogue);
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }   // warp-uniform, the warp stays converged
-        WQ_DIAG_ADD(d_wait);
         dequant_tile<LAYOUT, XT, GT, HAS_OFF>(sRaw_u32 + stage * C::kRawBytes, sB_u32 + slot * kWqBBytes, lg, sc2, of2,
                                               p, g, n_tile0);
         fence_proxy_async_smem();                      // generic-proxy stores -> visible to the MMA (async proxy)
@@ -529,7 +490,6 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         if (lane == 0) mbar_arrive(&aready[slot]);
       }
       it_base += kb1 - kb0;
-      WQ_DIAG_ADD(d_work);
       // The stop decision is taken by all dequantising warps together (named barrier 2).
       {
         bool got = ok && mbar_wait(tfull, tphase, abort_flag, kDevTimeoutEpilogue);
@@ -619,12 +579,8 @@ wq_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty);
-      WQ_DIAG_ADD(d_epi);
     }
     if (dw == 0 && lane == 0) {
-      WQ_DIAG_STORE(6, d_wait);
-      WQ_DIAG_STORE(7, d_work);
-      WQ_DIAG_STORE(8, d_epi);
     }
   }
 
@@ -751,16 +707,8 @@ WqPlan wq_plan(int64_t m, int64_t k, int64_t n) {
 template <int LAYOUT, typename XT, int MM, int NCH, bool HAS_OFF>
 int launch_wq(const CUtensorMap& tmW, const CUtensorMap& tmX, const WqParams& p, cudaStream_t st) {
   using C = WqCfg<LAYOUT, MM, NCH>;
-  auto kern = wq_umma_kernel<LAYOUT, XT, MM, NCH, HAS_OFF>;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kDynamic);
-    if (err != cudaSuccess)
-      return fail(B200Q_ERR_LAUNCH, "weight_quant_matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(err));
-    configured[dev] = true;
-  }
+  constexpr auto kern = wq_umma_kernel<LAYOUT, XT, MM, NCH, HAS_OFF>;
+  if (int rc = ensure_dynamic_smem<kern>(C::kDynamic, "weight_quant_matmul")) return rc;
   kern<<<p.ctas, kWqThreads, C::kDynamic, st>>>(tmW, tmX, p);
   if (int rc = check_launch("weight_quant_matmul (tcgen05)")) return rc;
   if (p.parts) {
@@ -882,9 +830,3 @@ extern "C" int b200q_weight_quant_matmul(const b200q_weight_quant_matmul_args* a
   if (a->x_dtype == B200Q_BF16) return dispatch_layout<__nv_bfloat16>(layout, pl.mm, tmW, tmX, p, st);
   return dispatch_layout<__half>(layout, pl.mm, tmW, tmX, p, st);
 }
-
-#ifdef B200Q_DIAG_TIMING
-extern "C" int b200q_diag_read(unsigned long long* out16) {
-  return cudaMemcpyFromSymbol(out16, b200q::g_wq_diag, sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : 3;
-}
-#endif

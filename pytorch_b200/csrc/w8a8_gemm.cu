@@ -40,6 +40,8 @@ enum EpiFlags : uint32_t {
   kOutVec = 16   // rows of `out` are 16-byte aligned: a thread may store 128-bit vectors
 };
 
+constexpr int kMaxDest = 8;   // GPUs of one node
+
 struct Epi {
   const void* scale;
   const float* offset;
@@ -51,6 +53,14 @@ struct Epi {
   int64_t ldo;      // row stride of `out` in elements (>= n)
   int scale_dtype, scale_bcast, offset_bcast, bias_dtype, out_dtype;
   uint32_t flags;
+  // Multi-GPU epilogues (peer-mapped destinations, plain stores over NVLink):
+  //   replicate (n_dest > 0, route_rows == 0): every finished element also goes to the same offset of
+  //       dest[0..n_dest), the peers' copies of `out`;
+  //   routed (route_rows > 0): row mm goes to row mm % route_rows of dest[mm / route_rows] (one of them
+  //       may be local memory); `out` is not written.
+  void* dest[kMaxDest];
+  int n_dest;
+  int64_t route_rows;
 };
 
 struct Sched {
@@ -96,6 +106,7 @@ __device__ __forceinline__ int to_int8(float v) { return max(-128, min(127, __fl
 __device__ __forceinline__ void store_one(const Epi& e, int64_t idx, int acc, int ib, float v) {
   switch (e.out_dtype) {
     case B200Q_I32: static_cast<int*>(e.out)[idx] = acc + ib; break;
+    case B200Q_F32: static_cast<float*>(e.out)[idx] = v; break;
     case B200Q_I8: static_cast<int8_t*>(e.out)[idx] = (int8_t)to_int8(v); break;
     default: static_cast<unsigned short*>(e.out)[idx] = (unsigned short)to_bits16(v, e.out_dtype); break;
   }
@@ -154,6 +165,18 @@ __device__ __forceinline__ void store_token_rows(const Epi& e, uint32_t taddr, i
         for (int q = 0; q < CH / 4; ++q)
           dst[q] = make_uint4(r[4 * q] + col_i[c * CH + 4 * q], r[4 * q + 1] + col_i[c * CH + 4 * q + 1],
                               r[4 * q + 2] + col_i[c * CH + 4 * q + 2], r[4 * q + 3] + col_i[c * CH + 4 * q + 3]);
+      } else if (e.out_dtype == B200Q_F32) {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<float*>(e.out) + mm * e.ldo + n0);
+#pragma unroll
+        for (int q = 0; q < CH / 4; ++q) {
+          uint32_t w[4];
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const int cj = c * CH + 4 * q + b;
+            w[b] = __float_as_uint(dequant((int)r[4 * q + b], col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags));
+          }
+          dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
       } else if (e.out_dtype == B200Q_I8) {
         uint32_t packed[CH / 4];
 #pragma unroll
@@ -200,6 +223,80 @@ __device__ __forceinline__ void store_token_rows(const Epi& e, uint32_t taddr, i
   }
 }
 
+// Epilogue of one accumulator tile for the multi-GPU forms (Epi::dest).  The calling warp owns the 32 token
+// rows starting at row0 (lane = row).  Results pass through a 4 KB shared-memory staging area private to
+// the warp, 128 bytes of every row at a time (64 16-bit or 32 32-bit outputs), so that eight lanes then
+// write one full 128-byte line of a row and a warp instruction covers four rows: full lines keep the
+// NVLink packets of the remote stores dense.  16-byte chunks are XOR-swizzled by the row so that both
+// the row-wise writes and the line-wise reads are free of bank conflicts.  Requires out_dtype in
+// {bf16, f16, f32, i32}, n a multiple of the 128-byte slab and 16-byte aligned destinations.
+template <int BN>
+__device__ __forceinline__ void store_token_rows_push(const Epi& e, uint32_t taddr, int64_t row0, int lane,
+                                                      int64_t n_tile0, const float* col_f0, const float* col_f1,
+                                                      const float* col_f2, const int* col_i, uint32_t stage) {
+  const int64_t mm = row0 + lane;
+  const bool mv = mm < e.m;
+  const float pt = (mv && (e.flags & kHasPt)) ? __ldg(e.pertoken + mm) : 1.0f;
+  const bool wide = e.out_dtype == B200Q_F32 || e.out_dtype == B200Q_I32;
+  const int ob = wide ? 4 : 2;
+  const int slab = wide ? 32 : 64;                       // columns per 128-byte slab
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += slab) {
+    if (n_tile0 + c0 >= e.n) break;                      // same decision in every lane
+    uint32_t w[32];                                      // this row's 128 bytes
+    if (wide) {
+      uint32_t r[32];
+      __syncwarp();
+      tmem_ld_x32(taddr + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int cj = c0 + j;
+        w[j] = e.out_dtype == B200Q_I32
+                   ? r[j] + (uint32_t)col_i[cj]
+                   : __float_as_uint(dequant((int)r[j], col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags));
+      }
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_x32(taddr + c0 + 32 * h, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const int cj = c0 + 32 * h + j;
+          const float v0 = dequant((int)r[j], col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags);
+          const float v1 = dequant((int)r[j + 1], col_i[cj + 1], col_f0[cj + 1], pt, col_f2[cj + 1], col_f1[cj + 1], e.flags);
+          w[16 * h + j / 2] = to_bits16(v0, e.out_dtype) | (to_bits16(v1, e.out_dtype) << 16);
+        }
+      }
+    }
+    __syncwarp();                                        // the previous slab has been read out
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      st_shared_v4(stage + lane * 128 + ((c ^ (lane & 7)) << 4), make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
+    __syncwarp();
+    const int ch = lane & 7;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = 4 * i + (lane >> 3);
+      const uint4 v = ld_shared_v4(stage + rr * 128 + ((ch ^ (rr & 7)) << 4));
+      const int64_t row = row0 + rr;
+      if (row >= e.m) continue;
+      if (e.route_rows > 0) {
+        const int64_t d = row / e.route_rows, lr = row - d * e.route_rows;
+        *reinterpret_cast<uint4*>(static_cast<uint8_t*>(e.dest[d]) + (lr * e.ldo + n_tile0 + c0) * ob + ch * 16) = v;
+      } else {
+        const int64_t off = (row * e.ldo + n_tile0 + c0) * ob + ch * 16;
+        *reinterpret_cast<uint4*>(static_cast<uint8_t*>(e.out) + off) = v;
+#pragma unroll 1
+        for (int p = 0; p < e.n_dest; ++p) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(e.dest[p]) + off) = v;
+      }
+    }
+  }
+}
+
 // Per-channel parameters of the BN columns starting at n_tile0 -> shared memory, by the epilogue threads.
 template <int BN>
 __device__ __forceinline__ void stage_channel_params(const Epi& e, int64_t n_tile0, int et, float* col_f0, float* col_f1,
@@ -222,7 +319,8 @@ struct SmemLayout {
   static constexpr int kBarOff = kTiles;                       // full[S], empty[S], tfull[2], tempty[2]
   static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;   // tmem base, abort flag
   static constexpr int kColOff = kMiscOff + 16;                // 4 x BN 32-bit column parameters
-  static constexpr int kTotal = kColOff + 4 * BN * 4;
+  static constexpr int kPushOff = (kColOff + 4 * BN * 4 + 127) & ~127;   // 4 KB per epilogue warp (multi-GPU epilogue)
+  static constexpr int kTotal = kPushOff + (kEpiThreads / 32) * 4096;
   static constexpr int kDynamic = kTotal + 1024;               // slack to align the tiles to 1024 B
 };
 
@@ -384,8 +482,18 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       } else {
         // D rows are tokens (m), D columns are channels (n).
-        store_token_rows<BN, CH>(e, taddr, (int64_t)ta * kTileA + row_in_tile, (int64_t)tb * BN, col_f0, col_f1, col_f2,
-                                 col_i);
+        if constexpr (BN >= 64) {
+          if (e.n_dest > 0) {
+            store_token_rows_push<BN>(e, taddr, (int64_t)ta * kTileA + quad * 32, lane, (int64_t)tb * BN, col_f0, col_f1,
+                                      col_f2, col_i, smem_u32(smem + L::kPushOff) + (warp - 2) * 4096);
+          } else {
+            store_token_rows<BN, CH>(e, taddr, (int64_t)ta * kTileA + row_in_tile, (int64_t)tb * BN, col_f0, col_f1,
+                                     col_f2, col_i);
+          }
+        } else {
+          store_token_rows<BN, CH>(e, taddr, (int64_t)ta * kTileA + row_in_tile, (int64_t)tb * BN, col_f0, col_f1, col_f2,
+                                   col_i);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -421,7 +529,8 @@ struct PairLayout {
   static constexpr int kBarOff = kTiles;
   static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;
   static constexpr int kColOff = kMiscOff + 16;
-  static constexpr int kTotal = kColOff + 4 * kBN * 4;
+  static constexpr int kPushOff = (kColOff + 4 * kBN * 4 + 127) & ~127;
+  static constexpr int kTotal = kPushOff + (kEpiThreads / 32) * 4096;
   static constexpr int kDynamic = kTotal + 1024;
 };
 
@@ -541,8 +650,13 @@ w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (!epilogue_all(mbar_wait(&tfull[buf], tphase, abort_flag, kDevTimeoutEpilogue))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
-      store_token_rows<BN, CH>(e, taddr, (int64_t)ta * 256 + rank * 128 + row_in_tile, (int64_t)tb * BN, col_f0, col_f1,
-                               col_f2, col_i);
+      if (e.n_dest > 0) {
+        store_token_rows_push<BN>(e, taddr, (int64_t)ta * 256 + rank * 128 + quad * 32, lane, (int64_t)tb * BN, col_f0,
+                                  col_f1, col_f2, col_i, smem_u32(smem + L::kPushOff) + (warp - 2) * 4096);
+      } else {
+        store_token_rows<BN, CH>(e, taddr, (int64_t)ta * 256 + rank * 128 + row_in_tile, (int64_t)tb * BN, col_f0, col_f1,
+                                 col_f2, col_i);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[buf]), 0));
@@ -558,6 +672,220 @@ w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     __syncwarp();
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decode shapes (M <= 128) in one launch: swapped operands as above (weight rows on the 128-row MMA axis,
+// tokens padded to BN), and K split across the CTAs of a thread-block cluster instead of across
+// independent CTAs.  Each CTA of a cluster accumulates its K range of the same 128-channel tile in its
+// own TMEM; the non-leader CTAs then park their int32 partial tile in their shared memory, the leader
+// adds them through distributed shared memory (coalesced ld.shared::cluster, lanes = channels) and runs
+// the dequantising epilogue.  No scratch in global memory, no atomics, no second kernel.  Clusters are
+// persistent and stride over the channel tiles.
+template <int BN, int STAGES>
+struct DecodeLayout {
+  static constexpr int kBTileBytes = BN * kBK;
+  static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+  static constexpr int kTiles = STAGES * kStageBytes;
+  static constexpr int kRedOff = kTiles;                            // [BN][128] int32: this CTA's partial tile
+  static constexpr int kBarOff = kRedOff + BN * 128 * 4;            // full[S], empty[S], tfull[2], tempty[2], red_ready, red_free
+  static constexpr int kMiscOff = kBarOff + (2 * STAGES + 6) * 8;   // tmem base, abort flag
+  static constexpr int kColOff = kMiscOff + 16;                     // pertoken[BN]
+  static constexpr int kTotal = kColOff + BN * 4;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+w8a8_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Epi e,
+                   const Sched s) {
+  using L = DecodeLayout<BN, STAGES>;
+  constexpr int CH = BN < 32 ? 16 : 32;
+  constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  static_assert(L::kDynamic > 116 * 1024 && L::kDynamic <= 227 * 1024, "one CTA per SM; shared memory budget");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * kATileBytes;
+  int32_t* red = reinterpret_cast<int32_t*>(smem + L::kRedOff);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint64_t* red_ready = tempty + 2;     // leader: every other CTA of the cluster has parked its partial tile
+  uint64_t* red_free = red_ready + 1;   // others: the leader has read this CTA's partial tile
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
+  float* col_pt = reinterpret_cast<float*>(smem + L::kColOff);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t crank = cluster_ctarank(), csize = cluster_nctarank();
+  const int cluster = (int)cluster_id_x(), nclusters = (int)nclusters_x();
+  // This CTA's K range (the same for every tile).
+  const int kb0 = (int)crank * s.kb_per_split, kb1 = min(s.kblocks, kb0 + s.kb_per_split);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], kEpiThreads / 32);
+    }
+    mbar_init(red_ready, csize > 1 ? csize - 1 : 1);
+    mbar_init(red_free, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&tmA);
+    prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (csize > 1) cluster_sync_all();     // the peers' barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const uint64_t pol_w = policy_evict_first();      // weights are streamed once
+      for (int u = cluster; u < s.units && ok; u += nclusters) {
+        const int ta = u % s.tiles_a, tb = u / s.tiles_a;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, kDevTimeoutProducer)) { ok = false; break; }
+          mbar_arrive_expect_tx(&full[stage], L::kStageBytes);
+          tma_load_2d_hint(sA + stage * kATileBytes, &tmA, &full[stage], kb * kBK, ta * kTileA, pol_w);
+          tma_load_2d(sB + stage * L::kBTileBytes, &tmB, &full[stage], kb * kBK, tb * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok)
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(2 /*s32*/, 1 /*s8*/, 1 /*s8*/, 0, 0, kTileA, BN);
+      int stage = 0, buf = 0;
+      uint32_t phase = 0, tphase = 0;
+      bool ok = true;
+      for (int u = cluster; u < s.units && ok; u += nclusters) {
+        if (!mbar_wait(&tempty[buf], tphase ^ 1, abort_flag, kDevTimeoutMma)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, kDevTimeoutMma)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc(smem_u32(sA + stage * kATileBytes), 16, 1024, kSwizzle128B);
+          const uint64_t bdesc = make_smem_desc(smem_u32(sB + stage * L::kBTileBytes), 16, 1024, kSwizzle128B);
+#pragma unroll
+          for (int k4 = 0; k4 < kBK / 32; ++k4)
+            umma_i8(d_tmem, adesc + 2 * k4, bdesc + 2 * k4, idesc, (kb > kb0 || k4 > 0) ? 1u : 0u);
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[buf]);
+        if (++buf == 2) { buf = 0; tphase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue / cluster reduction
+    const int et = threadIdx.x - 64;
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;          // channel row of the tile owned by this thread
+    int buf = 0;
+    uint32_t tphase = 0, rphase = 0;
+    for (int u = cluster; u < s.units; u += nclusters) {
+      const int ta = u % s.tiles_a, tb = u / s.tiles_a;
+      if (crank == 0) {
+        named_barrier_sync(1, kEpiThreads);
+        for (int i = et; i < BN; i += kEpiThreads) {
+          const int64_t mm = (int64_t)tb * BN + i;
+          col_pt[i] = ((e.flags & kHasPt) && mm < e.m) ? __ldg(e.pertoken + mm) : 1.0f;
+        }
+        named_barrier_sync(1, kEpiThreads);
+      }
+      if (!epilogue_all(mbar_wait(&tfull[buf], tphase, abort_flag, kDevTimeoutEpilogue))) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
+      if (crank != 0) {
+        // Park the partial tile: red[col][row], lanes write consecutive words.
+        if (!epilogue_all(mbar_wait(red_free, rphase ^ 1, abort_flag, kDevTimeoutEpilogue))) break;
+#pragma unroll 1
+        for (int c = 0; c < BN / CH; ++c) {
+          uint32_t r[CH];
+          __syncwarp();
+          tmem_ld_chunk<CH>(taddr + c * CH, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < CH; ++j) red[(c * CH + j) * 128 + row_in_tile] = (int32_t)r[j];
+        }
+        fence_acq_rel_cluster();
+        named_barrier_sync(1, kEpiThreads);
+        if (et == 0) mbar_arrive_cluster(map_to_cta(smem_u32(red_ready), 0));
+        rphase ^= 1;
+      } else {
+        if (csize > 1 && !epilogue_all(mbar_wait_cluster(red_ready, rphase, abort_flag, kDevTimeoutEpilogue))) break;
+        rphase ^= 1;
+        const int64_t n = (int64_t)ta * kTileA + row_in_tile;
+        const bool nv = n < e.n;
+        const float sc = nv ? load_scale(e, n) : 0.0f, off = nv ? load_offset(e, n) : 0.0f;
+        const float fb = nv ? load_float_bias(e, n) : 0.0f;
+        const int ib = nv ? load_int_bias(e, n) : 0;
+        const uint32_t red_addr = smem_u32(red) + row_in_tile * 4;
+#pragma unroll 1
+        for (int c = 0; c < BN / CH; ++c) {
+          uint32_t r[CH];
+          __syncwarp();
+          tmem_ld_chunk<CH>(taddr + c * CH, r);
+          tmem_ld_wait();
+          for (uint32_t p = 1; p < csize; ++p) {
+            const uint32_t base = map_to_cta(red_addr + (uint32_t)(c * CH) * 512u, p);
+#pragma unroll
+            for (int j = 0; j < CH; ++j) r[j] += ld_shared_cluster_u32(base + j * 512);
+          }
+          if (nv) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int64_t mm = (int64_t)tb * BN + c * CH + j;
+              if (mm < e.m) {
+                const int acc = (int)r[j];
+                store_one(e, mm * e.ldo + n, acc, ib, dequant(acc, ib, sc, col_pt[c * CH + j], fb, off, e.flags));
+              }
+            }
+          }
+        }
+        if (csize > 1) {
+          named_barrier_sync(1, kEpiThreads);         // every thread has finished reading the peers' tiles
+          if (et > 0 && et < (int)csize) mbar_arrive_cluster(map_to_cta(smem_u32(red_free), (uint32_t)et));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[buf]);
+      if (++buf == 2) { buf = 0; tphase ^= 1; }
+    }
+  }
+
+  // Teardown: no CTA leaves while a peer may still read its partial tile or signal its barriers.
+  tc_fence_before();
+  __syncthreads();
+  if (csize > 1) cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -616,57 +944,77 @@ template <int BN, int STAGES, bool SWAP>
 int launch_umma(const CUtensorMap& tmA, const CUtensorMap& tmB, const Epi& e, const Sched& s, cudaStream_t st) {
   using L = SmemLayout<BN, STAGES>;
   static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
-  auto kern = w8a8_umma_kernel<BN, STAGES, SWAP>;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
-    if (err != cudaSuccess) return fail(B200Q_ERR_LAUNCH, "quant_matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(err));
-    configured[dev] = true;
-  }
+  constexpr auto kern = w8a8_umma_kernel<BN, STAGES, SWAP>;
+  if (int rc = ensure_dynamic_smem<kern>(L::kDynamic, "quant_matmul")) return rc;
   const int grid = s.units < sm_count() ? s.units : sm_count();
   kern<<<grid, kThreads, L::kDynamic, st>>>(tmA, tmB, e, s);
   return check_launch("quant_matmul (tcgen05)");
 }
 
-template <int STAGES>
-int launch_umma_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Epi& e, const Sched& s, cudaStream_t st) {
-  using L = PairLayout<STAGES>;
-  auto kern = w8a8_umma_pair_kernel<STAGES>;
-  static bool configured[64] = {};
+// Number of clusters of `csize` CTAs of `kern` that can be resident at once (cached per device and size).
+template <auto Kern>
+int resident_clusters(int csize, int dynamic_smem) {
+  static std::mutex mu;
+  static int cached[64][9] = {};
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
-    if (err != cudaSuccess) return fail(B200Q_ERR_LAUNCH, "quant_matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(err));
-    configured[dev] = true;
-  }
-  // As many pairs as can be resident at once (a GPC with an odd number of free SMs leaves one unpaired).
-  static int resident_pairs[64] = {};
-  if (dev >= 0 && dev < 64 && resident_pairs[dev] == 0) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || csize < 1 || csize > 8) return sm_count() / (csize > 0 ? csize : 1);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev][csize] == 0) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    cfg.gridDim = dim3(csize * (sm_count() / csize));
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = L::kDynamic;
+    cfg.dynamicSmemBytes = dynamic_smem;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.x = csize;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, Kern, &cfg) != cudaSuccess || n <= 0) {
       cudaGetLastError();
-      n = sm_count() / 2;
+      n = sm_count() / csize;
     }
-    resident_pairs[dev] = n < sm_count() / 2 ? n : sm_count() / 2;
+    cached[dev][csize] = n < sm_count() / csize ? n : sm_count() / csize;
   }
-  int pairs = (dev >= 0 && dev < 64) ? resident_pairs[dev] : sm_count() / 2;
+  return cached[dev][csize];
+}
+
+template <int STAGES>
+int launch_umma_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Epi& e, const Sched& s, cudaStream_t st) {
+  using L = PairLayout<STAGES>;
+  constexpr auto kern = w8a8_umma_pair_kernel<STAGES>;
+  if (int rc = ensure_dynamic_smem<kern>(L::kDynamic, "quant_matmul")) return rc;
+  // As many pairs as can be resident at once (a GPC with an odd number of free SMs leaves one unpaired).
+  int pairs = resident_clusters<kern>(2, L::kDynamic);
   if (s.units < pairs) pairs = s.units;
   kern<<<2 * pairs, kThreads, L::kDynamic, st>>>(tmA, tmB, e, s);   // cluster dims (2,1,1) are a kernel attribute
   return check_launch("quant_matmul (tcgen05, CTA pairs)");
+}
+
+template <int BN, int STAGES>
+int launch_decode(const CUtensorMap& tmA, const CUtensorMap& tmB, const Epi& e, const Sched& s, int csize, cudaStream_t st) {
+  using L = DecodeLayout<BN, STAGES>;
+  constexpr auto kern = w8a8_decode_kernel<BN, STAGES>;
+  if (int rc = ensure_dynamic_smem<kern>(L::kDynamic, "quant_matmul")) return rc;
+  int clusters = resident_clusters<kern>(csize, L::kDynamic);
+  if (s.units < clusters) clusters = s.units;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(csize * clusters);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = L::kDynamic;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = csize;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t err = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, e, s);
+  if (err != cudaSuccess) return fail(B200Q_ERR_LAUNCH, "quant_matmul (tcgen05, cluster split-K): %s", cudaGetErrorString(err));
+  return check_launch("quant_matmul (tcgen05, cluster split-K)");
 }
 
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
@@ -675,14 +1023,18 @@ size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 struct Plan {
   bool tensor_path;     // tcgen05 path usable
   bool transpose;       // contiguous [k,n] weight must be re-laid out as [n,k] first
-  bool swap;            // M <= 128
+  bool swap;            // M <= 128: weight rows on the MMA's 128-row axis
+  bool decode;          // swapped, K split across the CTAs of a cluster (one launch, no scratch)
   bool pair;            // CTA-pair kernel (256 x 256 tiles)
   int bn;               // B-operand tile rows
-  int splits;
+  int splits;           // swapped without clusters: K split across independent CTAs (int32 scratch + atomics)
+  int csize;            // decode: CTAs per cluster = K splits
   size_t ws_transpose, ws_acc;
 };
 
-Plan make_plan(int64_t m, int64_t k, int64_t n, int64_t sk, int64_t sn, const void* x1, const void* x2) {
+// `multi_gpu`: the epilogue also stores to peers (or routes rows); only the token-row epilogue can.
+Plan make_plan(int64_t m, int64_t k, int64_t n, int64_t sk, int64_t sn, const void* x1, const void* x2,
+               bool multi_gpu = false) {
   Plan p{};
   const bool kmajor = (sk == 1 || k == 1) && (sn >= k) && (sn % 16 == 0);
   const bool nmajor = (sn == 1 || n == 1) && (sk == n) && (n % 16 == 0);
@@ -692,30 +1044,52 @@ Plan make_plan(int64_t m, int64_t k, int64_t n, int64_t sk, int64_t sn, const vo
   if (!p.tensor_path) return p;
   p.transpose = !kmajor;
   p.ws_transpose = p.transpose ? align256((size_t)n * k) : 0;
-  p.swap = m <= 128;
+  p.swap = m <= 128 && !multi_gpu;
   p.splits = 1;
+  p.csize = 1;
+  const int sms = sm_count();
   if (p.swap) {
     p.bn = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
-    // Split K so that all SMs stream weights; cost = (weight bytes + atomic traffic) / SM utilisation.
-    const int sms = sm_count();
     const int64_t tiles = ceil_div(n, kTileA), kblocks = ceil_div(k, kBK);
+    // Cluster split-K: rounds of resident clusters times the K blocks each CTA streams, plus a tail that
+    // grows with the number of partial tiles the leader has to add.
     double best = 1e300;
-    for (int sp = 1; sp <= 32 && sp <= kblocks; ++sp) {
-      const int64_t per = ceil_div(kblocks, sp), eff_sp = ceil_div(kblocks, per);
-      if (eff_sp != sp) continue;
-      const int64_t units = tiles * sp;
-      const double util = (double)units / (double)(ceil_div(units, sms) * sms);
-      const double bytes = (double)k * n + (sp > 1 ? (double)sp * m * n * 8.0 : 0.0);
-      const double cost = bytes / util;
-      if (cost < best * 0.98) { best = cost; p.splits = sp; }
+    for (int c = 1; c <= 8 && c <= kblocks; c *= 2) {
+      const int64_t per = ceil_div(kblocks, c);
+      if (ceil_div(kblocks, per) != c) continue;          // every CTA of the cluster must own at least one K block
+      const int64_t clusters = sms / c;
+      const double cost = (double)ceil_div(tiles, clusters) * (double)per + 0.5 * c;
+      if (cost < best) { best = cost; p.csize = c; }
     }
-    p.ws_acc = p.splits > 1 ? align256((size_t)m * n * 4) : 0;
+    p.decode = tiles * p.csize * 2 >= sms;                // at least half of the SMs get work
+    const char* env = getenv("B200Q_W8A8_DECODE");
+    if (env) p.decode = env[0] != '0';
+    if (!p.decode) {
+      // Few channel tiles and a long K: split K over independent CTAs so that all SMs stream weights;
+      // cost = (weight bytes + atomic traffic) / SM utilisation.
+      p.csize = 1;
+      double bestc = 1e300;
+      for (int sp = 1; sp <= 32 && sp <= kblocks; ++sp) {
+        const int64_t per = ceil_div(kblocks, sp), eff_sp = ceil_div(kblocks, per);
+        if (eff_sp != sp) continue;
+        const int64_t units = tiles * sp;
+        const double util = (double)units / (double)(ceil_div(units, sms) * sms);
+        const double bytes = (double)k * n + (sp > 1 ? (double)sp * m * n * 8.0 : 0.0);
+        const double cost = bytes / util;
+        if (cost < bestc * 0.98) { bestc = cost; p.splits = sp; }
+      }
+      p.ws_acc = p.splits > 1 ? align256((size_t)m * n * 4) : 0;
+    }
   } else {
     p.bn = n <= 128 ? 128 : 256;
-    // CTA pairs pay off once there are enough 256 x 256 tiles to keep all pairs busy.
+    // CTA pairs (256 x 256 tiles, one per two SMs) against single CTAs (128 x BN tiles): both give an SM
+    // the same work per tile, the pair streams a third less into shared memory and runs about a tenth
+    // faster, so it wins whenever it does not need more rounds.
     const char* env = getenv("B200Q_W8A8_PAIR");
     const bool allow = env ? (env[0] != '0') : true;
-    p.pair = allow && m >= 512 && n >= 512 && ceil_div(m, 256) * ceil_div(n, 256) >= sm_count() / 2;
+    const int64_t t_pair = ceil_div(m, 256) * ceil_div(n, 256), t_one = ceil_div(m, kTileA) * ceil_div(n, p.bn);
+    const double cost_pair = (double)ceil_div(t_pair, sms / 2), cost_one = 1.1 * (double)ceil_div(t_one, sms);
+    p.pair = allow && m > 128 && n >= 256 && cost_pair <= cost_one;
   }
   return p;
 }
@@ -737,11 +1111,13 @@ extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream
   B200Q_REQUIRE(a != nullptr, B200Q_ERR_BAD_ARG, "quant_matmul: args is NULL");
   B200Q_REQUIRE(a->m >= 0 && a->k >= 0 && a->n >= 0, B200Q_ERR_BAD_ARG, "quant_matmul: negative size");
   if (a->m == 0 || a->n == 0) return B200Q_OK;
-  B200Q_REQUIRE(a->out != nullptr && a->scale != nullptr, B200Q_ERR_BAD_ARG, "quant_matmul: out or scale is NULL");
+  const bool routed = a->route_rows > 0;
+  const bool multi_gpu = routed || a->n_peer_out > 0;
+  B200Q_REQUIRE((a->out != nullptr || routed) && a->scale != nullptr, B200Q_ERR_BAD_ARG, "quant_matmul: out or scale is NULL");
   B200Q_REQUIRE(a->k == 0 || (a->x1 != nullptr && a->x2 != nullptr), B200Q_ERR_BAD_ARG, "quant_matmul: x1 or x2 is NULL");
   B200Q_REQUIRE(a->out_dtype == B200Q_I8 || a->out_dtype == B200Q_F16 || a->out_dtype == B200Q_BF16 ||
-                    a->out_dtype == B200Q_I32,
-                B200Q_ERR_UNSUPPORTED, "quant_matmul: output dtype enum %d is not int8/f16/bf16/int32", a->out_dtype);
+                    a->out_dtype == B200Q_I32 || a->out_dtype == B200Q_F32,
+                B200Q_ERR_UNSUPPORTED, "quant_matmul: output dtype enum %d is not int8/f16/bf16/int32/f32", a->out_dtype);
   B200Q_REQUIRE(a->scale_dtype == B200Q_F32 || a->scale_dtype == B200Q_BF16 || a->scale_dtype == B200Q_I64,
                 B200Q_ERR_UNSUPPORTED, "quant_matmul: scale must be f32, bf16 or i64 (dtype enum %d)", a->scale_dtype);
   B200Q_REQUIRE(a->scale_len == 1 || a->scale_len == a->n, B200Q_ERR_BAD_ARG,
@@ -765,12 +1141,28 @@ extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream
   e.bias_dtype = a->bias ? a->bias_dtype : B200Q_NONE; e.out_dtype = a->out_dtype;
   e.flags = (a->pertoken_scale ? kHasPt : 0u) | (a->offset ? kHasOff : 0u) |
             (a->bias ? (a->bias_dtype == B200Q_I32 ? kHasIntBias : kHasFloatBias) : 0u);
-  {
-    const int64_t ob = a->out_dtype == B200Q_I8 ? 1 : a->out_dtype == B200Q_I32 ? 4 : 2;
-    if (aligned(a->out, 16) && (e.ldo * ob) % 16 == 0) e.flags |= kOutVec;
-  }
+  const int64_t ob = a->out_dtype == B200Q_I8 ? 1 : (a->out_dtype == B200Q_I32 || a->out_dtype == B200Q_F32) ? 4 : 2;
+  if ((a->out == nullptr || aligned(a->out, 16)) && (e.ldo * ob) % 16 == 0) e.flags |= kOutVec;
 
-  Plan p = make_plan(a->m, a->k, a->n, a->x2_stride_k, a->x2_stride_n, a->x1, a->x2);
+  Plan p = make_plan(a->m, a->k, a->n, a->x2_stride_k, a->x2_stride_n, a->x1, a->x2, multi_gpu);
+  if (multi_gpu) {
+    // Peer destinations are written by the token-row epilogue of the tcgen05 kernels, 128 bytes of a row at a time.
+    const int n_dest = routed ? (int)ceil_div(a->m, a->route_rows) : a->n_peer_out;
+    B200Q_REQUIRE(a->peer_out != nullptr && n_dest >= 1 && n_dest <= kMaxDest, B200Q_ERR_BAD_ARG,
+                  "quant_matmul: %d peer destinations (1..%d allowed, with a non-NULL table)", n_dest, kMaxDest);
+    B200Q_REQUIRE(p.tensor_path, B200Q_ERR_UNSUPPORTED,
+                  "quant_matmul: peer destinations need operands that meet the TMA rules (k %% 16 == 0, 16-byte aligned)");
+    B200Q_REQUIRE(ob != 1 && (a->n * ob) % 128 == 0 && (e.flags & kOutVec), B200Q_ERR_UNSUPPORTED,
+                  "quant_matmul: peer destinations need a 16- or 32-bit output type, n*size a multiple of 128 bytes "
+                  "and 16-byte aligned rows");
+    for (int i = 0; i < n_dest; ++i) {
+      B200Q_REQUIRE(a->peer_out[i] != nullptr && aligned(a->peer_out[i], 16), B200Q_ERR_BAD_ARG,
+                    "quant_matmul: peer destination %d is NULL or misaligned", i);
+      e.dest[i] = a->peer_out[i];
+    }
+    e.n_dest = n_dest;
+    e.route_rows = routed ? a->route_rows : 0;
+  }
   if (!p.tensor_path) {
     dim3 block(32, 8), grid((unsigned)ceil_div(a->n, 32), (unsigned)ceil_div(a->m, 8));
     B200Q_REQUIRE(grid.y <= 65535, B200Q_ERR_UNSUPPORTED,
@@ -806,11 +1198,11 @@ extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream
   const int8_t* b_ptr = p.swap ? a->x1 : w_nk;
   const int64_t b_rows = p.swap ? a->m : a->n, b_pitch = p.swap ? a->k : w_pitch;
   CUtensorMap tmA, tmB;
-  if (int rc = make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_ptr, a->k, a_rows, a_pitch, kBK, kTileA,
-                            CU_TENSOR_MAP_SWIZZLE_128B, "quant_matmul (A operand)"))
+  if (int rc = make_tmap_2d_cached(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_ptr, a->k, a_rows, a_pitch, kBK, kTileA,
+                                   CU_TENSOR_MAP_SWIZZLE_128B, "quant_matmul (A operand)"))
     return rc;
-  if (int rc = make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_ptr, a->k, b_rows, b_pitch, kBK,
-                            p.pair ? 128 : p.bn, CU_TENSOR_MAP_SWIZZLE_128B, "quant_matmul (B operand)"))
+  if (int rc = make_tmap_2d_cached(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_ptr, a->k, b_rows, b_pitch, kBK,
+                                   p.pair ? 128 : p.bn, CU_TENSOR_MAP_SWIZZLE_128B, "quant_matmul (B operand)"))
     return rc;
   if (p.pair) {
     Sched sp{};
@@ -827,6 +1219,17 @@ extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream
   s.tiles_a = (int)ceil_div(a_rows, kTileA);
   s.tiles_b = (int)ceil_div(b_rows, p.bn);
   s.kblocks = (int)ceil_div(a->k, kBK);
+  if (p.decode) {
+    s.kb_per_split = (int)ceil_div(s.kblocks, p.csize);
+    s.splits = p.csize;
+    s.units = s.tiles_a * s.tiles_b;
+    switch (p.bn) {
+      case 16: return launch_decode<16, 8>(tmA, tmB, e, s, p.csize, st);
+      case 32: return launch_decode<32, 8>(tmA, tmB, e, s, p.csize, st);
+      case 64: return launch_decode<64, 6>(tmA, tmB, e, s, p.csize, st);
+      default: return launch_decode<128, 4>(tmA, tmB, e, s, p.csize, st);
+    }
+  }
   s.kb_per_split = (int)ceil_div(s.kblocks, p.splits);
   s.splits = (int)ceil_div(s.kblocks, s.kb_per_split);
   const int64_t units = (int64_t)s.tiles_a * s.tiles_b * s.splits;

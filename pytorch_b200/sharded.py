@@ -6,11 +6,15 @@ their operand (``:495-500``): rank r of g holds rows ``[r*N/g, (r+1)*N/g)`` of t
 weight and the matching slice of ``scale`` / ``offset`` / ``bias``; activations, smooth scales
 and the per-token scale are replicated.  The only exchange step is an all-gather of the
 ``[M, N/g]`` outputs along N, which the reference issues as ``hcclAllGather``
-(``torch_npu/csrc/distributed/ProcessGroupHCCL.cpp:5896-5956``) and which runs here as
-``ncclAllGather`` over NVLink through ``torch.distributed``.  With a world size of one no
-collective is issued.
+(``torch_npu/csrc/distributed/ProcessGroupHCCL.cpp:5896-5956``).  Here the GEMM kernel itself
+stores every finished tile into the peers' matrices over NVLink (``peer_out`` of the C ABI), so
+the exchange overlaps the main loop, and one bounded cross-rank barrier ends the step.  An NCCL
+all-gather variant is kept for set-ups without peer-mapped memory.  With a world size of one no
+exchange is issued.
 """
 from __future__ import annotations
+
+import ctypes as C
 
 import torch
 import torch.distributed as dist
@@ -32,7 +36,7 @@ def shard_weight(weight_nk: torch.Tensor, *per_channel: torch.Tensor | None, ran
 
 
 class ColumnShardedOutput:
-    """Reusable buffers for gathering ``[M, N/g]`` shards into ``[M, N]``.
+    """Reusable buffers for gathering ``[M, N/g]`` shards into ``[M, N]`` with NCCL.
 
     ``all_gather_into_tensor`` delivers ``[g, M, N/g]`` (rank-major); one strided copy
     re-interleaves the column blocks into the row-major ``[M, N]`` the caller expects."""
@@ -55,53 +59,129 @@ class ColumnShardedOutput:
         return self.full
 
 
-class PeerColumnGather:
-    """The same exchange without NCCL and without the re-interleave copy: every rank keeps its
-    ``[M, N]`` result in symmetric (peer-mapped) memory, the GEMM writes the rank's column block
-    straight into the local matrix (``out_row_stride = N``), ``b200q_scatter_columns`` pushes that
-    block into every peer's matrix over NVLink with plain 128-bit stores, and a device-side barrier
-    on the symmetric-memory signal pads tells every rank that all blocks have landed.
+def _ptr_array(ptrs):
+    return (C.c_void_p * max(len(ptrs), 1))(*[C.c_void_p(int(p)) for p in ptrs])
 
-    Usage per step: ``y = self.local_block()`` (a ``[M, N/g]`` view to hand to the GEMM as ``out``),
-    then ``full = self.gather()``.  ``full`` is overwritten by the next step's pushes: finish reading
-    it (or copy it) before any rank starts that step.  No rank may leave while a step is in flight."""
 
-    def __init__(self, m: int, n: int, dtype: torch.dtype, device, group=None):
+class PeerGroup:
+    """The ranks of one node that address each other's memory, plus the cross-rank barrier
+    (``b200q_peer_barrier``) over a small array of flag words in peer-mapped memory.
+
+    The barrier kernel has a time budget (10 s unless ``timeout_ns`` says otherwise): when a peer never
+    arrives the kernel records a code in the device error word and returns, so a rank whose peer has
+    died gets a ``B200QError`` from :meth:`check` instead of a spinning kernel."""
+
+    def __init__(self, device, group=None):
         import torch.distributed._symmetric_memory as symm_mem
+        self._symm = symm_mem
         self.group = dist.group.WORLD if group is None else group
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
+        self.device = device
+        self.flags = symm_mem.empty((64,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
+        self._flags_handle = symm_mem.rendezvous(self.flags, self.group)
+        dist.barrier(self.group)                      # every rank's flags are zero before anyone signals
+        self._flag_ptrs = _ptr_array(self._flags_handle.buffer_ptrs)
+        self.epoch = 0
+
+    def symmetric(self, shape, dtype):
+        """A tensor in peer-mapped memory and the device addresses of every rank's copy."""
+        t = self._symm.empty(tuple(shape), dtype=dtype, device=self.device)
+        handle = self._symm.rendezvous(t, self.group)
+        return t, list(handle.buffer_ptrs), handle
+
+    def peers_after(self, ptrs, byte_offset: int = 0):
+        """The other ranks' pointers in a rank-staggered order (rank r starts with r+1), so that at any
+        moment the ranks write to different peers and the switch sees an all-to-all, not a hot spot."""
+        return [int(ptrs[(self.rank + 1 + i) % self.world]) + byte_offset for i in range(self.world - 1)]
+
+    def barrier(self, timeout_ns: int = 0) -> None:
+        from . import _cabi
+        self.epoch += 1
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _cabi.check(_cabi.lib().b200q_peer_barrier(self._flag_ptrs, self.world, self.rank, self.epoch & 0xFFFFFFFF,
+                                                   timeout_ns, st))
+
+    def check(self) -> None:
+        """Raises if a kernel on this device gave up a bounded wait (synchronises the device)."""
+        from . import _cabi
+        code = _cabi.device_error(reset=True)
+        if code:
+            raise _cabi.B200QError(_cabi.ERR_DEVICE, f"a kernel gave up a bounded wait (device error 0x{code:x})")
+
+
+class PeerColumnGather:
+    """``[M, N]`` result matrices in peer-mapped memory, ``buffers`` of them used in rotation.
+
+    Per step the caller takes ``local_block()`` (the ``[M, N/g]`` view of the current matrix the GEMM
+    writes) and ``peer_blocks()`` (the addresses of the same block in every peer's current matrix, which
+    the GEMM's epilogue writes too), runs the GEMM, and ends the step with ``finish()``: one barrier,
+    after which ``full`` holds every rank's columns.  With two buffers the matrix a step has produced
+    stays untouched while the next step runs: peers only write into it again two steps later, and by
+    then the barrier in between has ordered that after everything this rank had queued on its stream
+    before it, a device-to-host copy of ``full`` included."""
+
+    def __init__(self, m: int, n: int, dtype: torch.dtype, device, peers: PeerGroup | None = None, group=None,
+                 buffers: int = 2):
+        self.peers = peers if peers is not None else PeerGroup(device, group)
+        self.world, self.rank = self.peers.world, self.peers.rank
         self.m, self.n = m, n
         self.lo, self.hi = shard_bounds(n, self.rank, self.world)
-        self.full = symm_mem.empty((m, n), dtype=dtype, device=device)
-        self.handle = symm_mem.rendezvous(self.full, self.group)
-        ptrs = list(self.handle.buffer_ptrs)
-        # staggered order: rank r starts with r+1, so the switch sees an all-to-all, not a hot spot
-        self.peer_ptrs = [ptrs[(self.rank + 1 + i) % self.world] for i in range(self.world - 1)]
+        self.es = torch.empty((), dtype=dtype).element_size()
+        self.bufs = []
+        for _ in range(buffers):
+            t, ptrs, handle = self.peers.symmetric((m, n), dtype)
+            self.bufs.append((t, ptrs, handle))
+        self.cur = 0
+
+    @property
+    def full(self) -> torch.Tensor:
+        return self.bufs[self.cur][0]
+
+    @property
+    def peer_ptrs(self):
+        return self.peers.peers_after(self.bufs[self.cur][1])
+
+    def advance(self) -> None:
+        self.cur = (self.cur + 1) % len(self.bufs)
 
     def local_block(self) -> torch.Tensor:
         return self.full[:, self.lo:self.hi]
 
-    def gather(self) -> torch.Tensor:
+    def peer_blocks(self):
+        return self.peers.peers_after(self.bufs[self.cur][1], self.lo * self.es)
+
+    def push(self) -> None:
+        """Stand-alone push of the current block (for a producer that could not write to the peers itself)."""
         from . import _cabi
         _cabi.scatter_columns(self.full, self.peer_ptrs, self.lo, self.hi)
-        self.handle.barrier(channel=0)
+
+    def finish(self) -> torch.Tensor:
+        self.peers.barrier()
         return self.full
+
+    def gather(self) -> torch.Tensor:
+        """Push kernel + barrier: the exchange as a separate step after a GEMM that wrote only locally."""
+        self.push()
+        return self.finish()
 
 
 class ShardedW8A8LinearPlan:
     """One column-sharded W8A8 linear with every buffer and C-ABI argument block prepared once:
-    dynamic quant of ``x`` (replicated), GEMM of this rank's columns written straight into the
-    peer-mapped ``[M, N]`` matrix, push to the peers, barrier.  ``run()`` then issues four C-ABI
-    calls and one barrier with no allocation and almost no Python work, which matters when eight
-    ranks share one host and a step lasts about a millisecond."""
+    dynamic quant of ``x`` (replicated), then one GEMM launch that writes this rank's columns into the
+    local ``[M, N]`` matrix and into every peer's.  ``run()`` issues two C-ABI calls with no allocation
+    and almost no Python work, which matters when eight ranks share one host and a step lasts well under
+    a millisecond.  The caller ends the step with ``gather.finish()`` (one barrier for all linears of the
+    step that share a :class:`PeerGroup`)."""
 
     def __init__(self, x: torch.Tensor, smooth_scales: torch.Tensor, weight_nk_shard: torch.Tensor,
-                 scale_shard: torch.Tensor, gather: PeerColumnGather):
-        import ctypes as C
+                 scale_shard: torch.Tensor, gather: PeerColumnGather, fused_push: bool = True):
         from . import _cabi
-        self._C, self._cabi, self._lib = C, _cabi, _cabi.lib()
+        self._cabi, self._lib = _cabi, _cabi.lib()
         self.gather = gather
+        self.fused_push = fused_push
         m, k = x.shape
         n = weight_nk_shard.shape[0]
         assert m == gather.m and n == gather.hi - gather.lo and weight_nk_shard.shape[1] == k
@@ -112,40 +192,49 @@ class ShardedW8A8LinearPlan:
         self.w, self.scale = weight_nk_shard, scale_shard.contiguous()
         need = self._lib.b200q_quant_matmul_workspace_bytes(m, k, n, 1, k)
         self.ws = torch.empty(max(need, 1), dtype=torch.uint8, device=dev)
-        out = gather.local_block()
-        a = _cabi.QuantMatmulArgs()
-        a.x1, a.x2, a.m, a.k, a.n = self.q.data_ptr(), self.w.data_ptr(), m, k, n
-        a.x2_stride_k, a.x2_stride_n = 1, k
-        a.scale, a.scale_dtype, a.scale_len = self.scale.data_ptr(), _cabi.DTYPE[self.scale.dtype], self.scale.numel()
-        a.pertoken_scale, a.bias_dtype = self.s.data_ptr(), _cabi.NONE
-        a.out, a.out_dtype, a.out_row_stride = out.data_ptr(), _cabi.DTYPE[out.dtype], out.stride(0)
-        if need:
-            a.workspace, a.workspace_bytes = self.ws.data_ptr(), need
-        self.args = a
         self.m, self.k = m, k
-        es = gather.full.element_size()
-        self.peers = (C.c_void_p * max(len(gather.peer_ptrs), 1))(*[C.c_void_p(int(p)) for p in gather.peer_ptrs])
-        self.n_peers = len(gather.peer_ptrs)
-        self.row_bytes, self.col_off, self.block = gather.n * es, gather.lo * es, (gather.hi - gather.lo) * es
+        self.args, self._keep = [], []
+        for b in range(len(gather.bufs)):            # one argument block per result buffer
+            gather.cur = b
+            out = gather.local_block()
+            a = _cabi.QuantMatmulArgs()
+            a.x1, a.x2, a.m, a.k, a.n = self.q.data_ptr(), self.w.data_ptr(), m, k, n
+            a.x2_stride_k, a.x2_stride_n = 1, k
+            a.scale, a.scale_dtype, a.scale_len = self.scale.data_ptr(), _cabi.DTYPE[self.scale.dtype], self.scale.numel()
+            a.pertoken_scale, a.bias_dtype = self.s.data_ptr(), _cabi.NONE
+            a.out, a.out_dtype, a.out_row_stride = out.data_ptr(), _cabi.DTYPE[out.dtype], out.stride(0)
+            if need:
+                a.workspace, a.workspace_bytes = self.ws.data_ptr(), need
+            if fused_push and gather.world > 1:
+                arr = _ptr_array(gather.peer_blocks())
+                self._keep.append(arr)
+                a.peer_out, a.n_peer_out = arr, gather.world - 1
+            self.args.append(a)
+        gather.cur = 0
 
-    def run(self, x: torch.Tensor | None = None, exchange: bool = True) -> torch.Tensor:
-        C, cabi, lib = self._C, self._cabi, self._lib
+    def quant(self, x: torch.Tensor | None = None) -> None:
+        cabi = self._cabi
         xs = self.x if x is None else x
         st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-        cabi.check(lib.b200q_dynamic_quant(xs.data_ptr(), cabi.DTYPE[xs.dtype], self.smooth.data_ptr(),
-                                           cabi.DTYPE[self.smooth.dtype], self.q.data_ptr(), self.s.data_ptr(),
-                                           self.m, self.k, st))
-        cabi.check(lib.b200q_quant_matmul(C.byref(self.args), st))
-        if exchange:
-            cabi.check(lib.b200q_scatter_columns(self.gather.full.data_ptr(), self.peers, self.n_peers, self.m,
-                                                 self.row_bytes, self.col_off, self.block, st))
-            self.gather.handle.barrier(channel=0)
+        cabi.check(self._lib.b200q_dynamic_quant(xs.data_ptr(), cabi.DTYPE[xs.dtype], self.smooth.data_ptr(),
+                                                 cabi.DTYPE[self.smooth.dtype], self.q.data_ptr(), self.s.data_ptr(),
+                                                 self.m, self.k, st))
+
+    def matmul(self, push: bool = True) -> None:
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        self._cabi.check(self._lib.b200q_quant_matmul(C.byref(self.args[self.gather.cur]), st))
+        if push and not self.fused_push and self.gather.world > 1:
+            self.gather.push()
+
+    def run(self, x: torch.Tensor | None = None) -> torch.Tensor:
+        self.quant(x)
+        self.matmul()
         return self.gather.full
 
 
 def sharded_w8a8_linear(x: torch.Tensor, smooth_scales, weight_nk_shard: torch.Tensor, scale_shard: torch.Tensor,
                         gather: ColumnShardedOutput, *, output_dtype=torch.bfloat16, quantized=None):
-    """dynamic quant (replicated) -> W8A8 GEMM on this rank's columns -> all-gather along N.
+    """dynamic quant (replicated) -> W8A8 GEMM on this rank's columns -> all-gather along N (NCCL variant).
 
     ``quantized`` may carry the ``(int8, scale)`` pair of an earlier call on the same ``x``."""
     ops = torch.ops.npu

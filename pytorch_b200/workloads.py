@@ -149,3 +149,12 @@ def quant_matmul_bytes(m, k, n, out_bytes=2, pertoken=True, bias=False, offset=F
 def w4a16_bytes(m, k, n, gs):
     groups = k // gs if gs else 1
     return 2 * m * k + k * n // 2 + 2 * groups * n * 2 + 2 * m * n
+
+
+def config5_row_parallel_down(rank: int, world: int, *, hidden=C5_HIDDEN, ffn=C5_FFN, seed=5000):
+    """The down projection of the same MLP cut along K instead of N (the reference's tensor-parallel
+    form, ``npu_mm_reduce_scatter_base``): rank ``rank`` holds ``[hidden, ffn/world]`` of the ``[n,k]``
+    weight, the matching slice of the activation's columns, and its own per-channel scale."""
+    gs = _gen(seed + 101 + rank + 16 * world)
+    kr = ffn // world
+    return dict(down_weight_nk=rand_int8((hidden, kr), gs), down_scale=rand_uniform((hidden,), gs, 1e-3, 1e-2))

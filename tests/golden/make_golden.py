@@ -13,6 +13,8 @@ inputs.  The tests then require the oracle to reproduce those outputs:
                                         fp16 and bf16 outputs, with and without offset)
 * ``cpu_linear_weight_quant``           test/contrib/test_linear_weight_quant.py:20-28
 * ``_get_global_tensor`` (int8 dequant) test/distributed/tensor/test_matrix_ops.py:21-40
+* ``TestMmReduceScatterBaseOp._get_global_tensor`` (per-rank int8 products, dequantised and added in rank
+                                        order)  test/distributed/tensor/test_matrix_ops.py:86-110
 
 ``oracle_kat.npz`` holds known-answer vectors computed by ``oracle/quant_oracle.py``
 for config 1 and a few small cases, so that the GPU tests can be held against
@@ -107,6 +109,23 @@ def reference_goldens(ref):
     out["mm_x1"], out["mm_x2"] = x1.to(torch.int8).numpy(), x2.to(torch.int8).numpy()
     out["mm_bias"] = b.to(torch.int32).numpy()
     out["mm_s1"], out["mm_s2"], out["mm_out"] = s1.numpy(), s2.numpy(), deq.numpy()
+
+    # quantised reduce-scatter golden: three ranks, each with its own K slice and scales (own generator, so
+    # that the draws above keep their values)
+    ns4 = {"torch": torch}
+    exec(_cut(f_mm, "_get_global_tensor", "TestMmReduceScatterBaseOp"), ns4)
+    g4 = torch.Generator().manual_seed(79)
+    ranks, m, k, n = 3, 6, 48, 32
+    x1l = [torch.randint(-127, 128, (m, k), generator=g4).to(torch.int8) for _ in range(ranks)]
+    x2l = [torch.randint(-127, 128, (k, n), generator=g4).to(torch.int8) for _ in range(ranks)]
+    s1l = [torch.rand((m, 1), generator=g4) * 1e-2 for _ in range(ranks)]
+    s2l = [torch.rand((1, n), generator=g4) * 1e-2 for _ in range(ranks)]
+    _, _, rs = ns4["_get_global_tensor"](None, x1l, x2l, None, s1l, s2l)
+    out["rs_x1"] = torch.stack(x1l).numpy()
+    out["rs_x2"] = torch.stack(x2l).numpy()
+    out["rs_s1"] = torch.stack(s1l).numpy()
+    out["rs_s2"] = torch.stack(s2l).numpy()
+    out["rs_out"] = rs.numpy()
     np.savez_compressed(os.path.join(HERE, "reference_goldens.npz"), **out)
 
 

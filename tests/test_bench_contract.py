@@ -9,7 +9,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def run(env_extra):
-    env = dict(os.environ, **env_extra)
+    env = dict(os.environ, BENCH_CPU_SAMPLE_ROWS="64", **env_extra)     # a small sample keeps the CPU suite short
     return subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
                            "--warmup", "1", "--gpus", env_extra.get("WORLD_SIZE", "1")],
                           capture_output=True, text=True, env=env, timeout=600)

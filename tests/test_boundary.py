@@ -34,7 +34,7 @@ def test_cabi_exports_every_declared_symbol():
 
 def test_struct_layout_matches_header():
     from pytorch_b200 import _cabi
-    assert ctypes.sizeof(_cabi.QuantMatmulArgs) == 20 * 8
+    assert ctypes.sizeof(_cabi.QuantMatmulArgs) == 23 * 8
     assert ctypes.sizeof(_cabi.WeightQuantMatmulArgs) == 16 * 8
 
 
@@ -220,3 +220,32 @@ def test_module_signatures_and_dtype_gates(pkg):
     w.antiquant_scale.data = torch.empty(32, 2, dtype=torch.float16, device="meta")
     w.antiquant_offset.data = torch.empty(32, 2, dtype=torch.float16, device="meta")
     assert w(torch.empty(5, 64, dtype=torch.float16, device="meta")).shape == (5, 32)
+
+
+def test_collective_fused_operators_meta_contracts(pkg):
+    """Shape/dtype contracts of the collective-fused operators (reference: test/test_fake_tensor.py:1555-1583 for
+    npu_mm_all_reduce_base; schemas torch_npu/distributed/tensor/_matrix_ops.py:471-476,556-561)."""
+    x1 = torch.empty(128, 256, dtype=torch.int8, device="meta")
+    x2 = torch.empty(256, 128, dtype=torch.int8, device="meta")
+    out = pkg.npu_mm_all_reduce_base(x1, x2, "fake group info", reduce_op="sum",
+                                     dequant_scale=torch.empty(128, dtype=torch.int64, device="meta"))
+    assert out.shape == (128, 128) and out.dtype == torch.float16
+    out = pkg.npu_mm_all_reduce_base(x1, x2, "fake group info", reduce_op="sum",
+                                     dequant_scale=torch.empty(128, dtype=torch.bfloat16, device="meta"))
+    assert out.shape == (128, 128) and out.dtype == torch.bfloat16
+    out = pkg.npu_mm_reduce_scatter_base(x1, x2, "g", 4, x1_scale=torch.empty(128, 1, device="meta"),
+                                         x2_scale=torch.empty(1, 128, device="meta"), output_dtype=torch.bfloat16)
+    assert out.shape == (32, 128) and out.dtype == torch.bfloat16
+    out, gathered = pkg.npu_all_gather_base_mm(x1, x2, "g", 4)
+    assert out.shape == (512, 128) and gathered.shape == (512, 256) and gathered.dtype == torch.int8
+    s = str(torch.ops.npu.npu_mm_reduce_scatter_base.default._schema)
+    for kw in ("hcom", "world_size", "reduce_op", "bias", "x1_scale", "x2_scale", "comm_turn", "output_dtype", "comm_mode"):
+        assert kw in s
+    s = str(torch.ops.npu.npu_all_gather_base_mm.default._schema)
+    for kw in ("gather_index", "gather_output", "x1_scale", "x2_scale"):
+        assert kw in s
+
+
+def test_collective_fused_operators_have_no_cpu_path(pkg):
+    with pytest.raises(NotImplementedError):
+        pkg.npu_mm_reduce_scatter_base(torch.zeros(4, 16, dtype=torch.int8), torch.zeros(16, 8, dtype=torch.int8), "g", 2)

@@ -58,6 +58,24 @@ def test_quant_matmul_batched_x2_and_bias_shapes(pb):
     assert got.dtype == torch.int8 and torch.equal(got, oracle.quant_matmul(a, b, sc, offset=of, bias=bi))
 
 
+def test_quant_matmul_single_batch_x2_serves_every_batch_of_x1(pb):
+    """x1 [B>1, M, K] against x2 [1, K, N]: one weight for all batches, every row of the [B, M, N] output is
+    written (pertoken_scale has B*M elements, bias [1,1,N])."""
+    g = torch.Generator().manual_seed(12)
+    x1 = workloads.rand_int8((3, 20, 64), g)
+    x2 = workloads.rand_int8((1, 64, 48), g)
+    scale = workloads.rand_uniform((48,), g, 1e-3, 1e-2)
+    pt = workloads.rand_uniform((60,), g, 1e-3, 1e-2)
+    bias = torch.randint(-100, 100, (1, 1, 48), generator=g, dtype=torch.int32)
+    got = pb.npu_quant_matmul(x1.cuda(), x2.cuda(), scale.cuda(), pertoken_scale=pt.cuda(), bias=bias.cuda(),
+                              output_dtype=torch.bfloat16).cpu()
+    want = oracle.quant_matmul(x1.reshape(60, 64), x2[0], scale, pertoken_scale=pt, bias=bias.reshape(-1),
+                               output_dtype=torch.bfloat16).reshape(3, 20, 48)
+    assert got.shape == (3, 20, 48) and torch.equal(got.view(torch.int16), want.view(torch.int16))
+    acc = pb.npu_quant_matmul(x1.cuda(), x2.cuda(), scale.cuda(), output_dtype=torch.int32).cpu()
+    assert torch.equal(acc, oracle.quant_matmul(x1.reshape(60, 64), x2[0], scale, output_dtype=torch.int32).reshape(3, 20, 48))
+
+
 def test_linear_quant_module_equals_op_and_oracle(pb):
     from pytorch_b200.contrib.module import LinearA8W8Quant, LinearQuant
     g = torch.Generator().manual_seed(3)

@@ -266,3 +266,91 @@ def test_config4_batched_offset_bias_fp16(cabi):
     v = torch.randint(-3, 4, (n,), generator=g, dtype=torch.int64)
     rhs = d["x1"].reshape(-1, k).to(torch.int64) @ (d["x2"].to(torch.int64) @ v) + (d["bias"].to(torch.int64) @ v)
     assert torch.equal(acc.to(torch.int64) @ v, rhs)
+
+
+def test_dynamic_quant_tiny_rows_keep_ieee_division(cabi):
+    """Rows whose maximum is so small that 1/scale overflows (bf16 inputs reach 1e-38): the reciprocal path
+    must hand over to true division and still agree with the oracle bit for bit."""
+    g = torch.Generator().manual_seed(8)
+    for amp in (1e-38, 3e-37, 1e-33, 1e-28):
+        x = (torch.randn((5, 2048), generator=g) * amp).to(torch.bfloat16)
+        x[1] = 0
+        check_dq(cabi, x, None)
+        check_dq(cabi, x[:, :520].contiguous(), None)          # register kernel (k < 1024)
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 4096, 4096), (16, 8192, 2048), (7, 1024, 9472), (128, 1024, 22016),
+                                   (64, 11008, 4096), (32, 512, 9600), (100, 2048, 12288)])
+def test_quant_matmul_decode_cluster_split_k(cabi, m, k, n):
+    """M <= 128 with enough channel tiles: one launch, K split over a thread-block cluster (sizes 1, 2, 4
+    and 8 occur in this list), partial tiles added through distributed shared memory.  int32 accumulators in
+    full and the fused epilogue must match the oracle exactly."""
+    g = torch.Generator().manual_seed(m + k + n)
+    x1 = workloads.rand_int8((m, k), g, -128, 127)
+    w = workloads.rand_int8((n, k), g, -128, 127)
+    assert cabi.lib().b200q_quant_matmul_workspace_bytes(m, k, n, 1, k) == 0      # no scratch, no second kernel
+    got = cabi.quant_matmul(x1.cuda(), cuda_view(w), torch.ones(1, device="cuda"), output_dtype=torch.int32).cpu()
+    want = oracle.quant_matmul(x1, w.t(), torch.ones(1), output_dtype=torch.int32)
+    assert torch.equal(got, want), f"{(got != want).sum().item()} of {got.numel()} accumulators differ"
+    scale = workloads.rand_uniform((n,), g, 1e-3, 1e-2)
+    pt = workloads.rand_uniform((m,), g, 1e-3, 1e-2)
+    bias = torch.randint(-1000, 1001, (n,), generator=g, dtype=torch.int32)
+    check_qmm(cabi, x1, w.t(), scale, pertoken_scale=pt, bias=bias, output_dtype=torch.bfloat16)
+    for _ in range(3):                                          # persistent clusters reuse their barriers and buffers
+        again = cabi.quant_matmul(x1.cuda(), cuda_view(w), torch.ones(1, device="cuda"), output_dtype=torch.int32).cpu()
+        assert torch.equal(again, want)
+
+
+def freivalds_and_rows(cabi, q, qo, so, s, weight_nk, scale, seed, rows_checked=64):
+    """Full-size GEMM check: (X W) v == X (W v) on the int32 accumulators in int64, and `rows_checked` full
+    rows of the bf16 output against the oracle."""
+    m, n = q.shape[0], weight_nk.shape[0]
+    wv = cuda_view(weight_nk)
+    acc = cabi.quant_matmul(q, wv, torch.ones(1, device="cuda"), output_dtype=torch.int32)
+    g = torch.Generator().manual_seed(seed)
+    v = torch.randint(-3, 4, (n,), generator=g, dtype=torch.int64)
+    lhs = (acc.to(torch.float64) @ v.cuda().to(torch.float64)).cpu().to(torch.int64)       # |sum| < 2^53: exact
+    del acc
+    # W v and X (W v) in float64, a slice of W at a time: every partial sum is an integer below 2^53, so exact
+    k = weight_nk.shape[1]
+    wv_host = torch.zeros(k, dtype=torch.float64)
+    vf = v.to(torch.float64)
+    for lo in range(0, n, 8192):
+        wv_host += weight_nk[lo:lo + 8192].to(torch.float64).t() @ vf[lo:lo + 8192]
+    rhs = (qo.to(torch.float64) @ wv_host).to(torch.int64)
+    assert torch.equal(lhs, rhs), "Freivalds check of the int32 accumulators failed"
+    y = cabi.quant_matmul(q, wv, scale.cuda(), pertoken_scale=s, output_dtype=torch.bfloat16)
+    rows = torch.randperm(m, generator=g)[:rows_checked]
+    got = y[rows.cuda()].cpu()
+    del y
+    want = oracle.quant_matmul(qo[rows], weight_nk.t(), scale, pertoken_scale=so[rows], output_dtype=torch.bfloat16)
+    assert oracle.max_mixed_error(got, want) <= TOL
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+def test_config5_llama70b_mlp_full_size(cabi):
+    """Config 5 at full size on one GPU (the shapes the benchmark is quoted on): dynamic quant of x [4096,8192]
+    and x_down [4096,28672] compared with the oracle in full, bit for bit; gate/up GEMM 4096x8192x57344 and down
+    GEMM 4096x28672x8192 through the Freivalds product check on all int32 accumulators plus 64 full bf16 rows."""
+    d = workloads.config5_shard(0, 1)
+    q, s = cabi.dynamic_quant(d["x"].cuda(), d["smooth_scales"].cuda())
+    qo, so = oracle.dynamic_quant(d["x"], d["smooth_scales"])
+    assert torch.equal(s.cpu().view(torch.int32), so.view(torch.int32)) and torch.equal(q.cpu(), qo)
+    freivalds_and_rows(cabi, q, qo, so, s, d["gate_up_weight_nk"], d["gate_up_scale"], 51)
+    del q, s
+    q2, s2 = cabi.dynamic_quant(d["x_down"].cuda(), d["smooth_scales_down"].cuda())
+    q2o, s2o = oracle.dynamic_quant(d["x_down"], d["smooth_scales_down"])
+    assert torch.equal(s2.cpu().view(torch.int32), s2o.view(torch.int32)) and torch.equal(q2.cpu(), q2o)
+    freivalds_and_rows(cabi, q2, q2o, s2o, s2, d["down_weight_nk"], d["down_scale"], 52)
+
+
+def test_int4pack_flags_values_outside_int4(cabi):
+    w = torch.zeros(4, 16, dtype=torch.int32, device="cuda")
+    w[2, 5] = 9                                                 # no int4 representation
+    cabi.int4pack(w)
+    torch.cuda.synchronize()
+    assert cabi.device_error(reset=True) == 0x201
+    w[2, 5] = -8
+    cabi.int4pack(w)
+    torch.cuda.synchronize()
+    assert cabi.device_error() == 0

@@ -61,7 +61,8 @@ def _rank_main(rank, world, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TORCH_SYMM_MEM_DISABLE_MULTICAST="1",
                       NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
-    from pytorch_b200 import _cabi, sharded
+    import pytorch_b200 as pb
+    from pytorch_b200 import _cabi, collective_ops, sharded
     try:
         torch.cuda.set_device(rank)
         dev = torch.device("cuda", rank)
@@ -70,24 +71,69 @@ def _rank_main(rank, world, port, results):
         d = workloads.w8a8_linear(m, k, n, 77)
         q, s = oracle.dynamic_quant(d["x"], d["smooth_scales"])
         want = oracle.quant_matmul(q, d["x2"], d["scale"], pertoken_scale=s, output_dtype=torch.bfloat16)
-        gat = sharded.PeerColumnGather(m, n, torch.bfloat16, dev)
+        peers = sharded.PeerGroup(dev)
+        gat = sharded.PeerColumnGather(m, n, torch.bfloat16, dev, peers)
         w, sc = sharded.shard_weight(d["weight_nk"], d["scale"], rank=rank, world=world)
-        for _ in range(2):                                # buffers are reused from step to step
-            _cabi.quant_matmul(q.to(dev), w.to(dev).t(), sc.to(dev), pertoken_scale=s.to(dev),
-                               output_dtype=torch.bfloat16, out=gat.local_block())
-            full = gat.gather()
+        ok = True
+        # (a) separate push kernel after a GEMM that wrote locally; (b) the GEMM's own epilogue writes to the peer
+        for step in range(4):                             # result matrices and flags are reused from step to step
+            if step % 2 == 0:
+                _cabi.quant_matmul(q.to(dev), w.to(dev).t(), sc.to(dev), pertoken_scale=s.to(dev),
+                                   output_dtype=torch.bfloat16, out=gat.local_block())
+                full = gat.gather()
+            else:
+                _cabi.quant_matmul(q.to(dev), w.to(dev).t(), sc.to(dev), pertoken_scale=s.to(dev),
+                                   output_dtype=torch.bfloat16, out=gat.local_block(), peer_out=gat.peer_blocks())
+                full = gat.finish()
             torch.cuda.synchronize()
-            ok = torch.equal(full.cpu().view(torch.int16), want.view(torch.int16))
-            dist.barrier()
+            ok = ok and torch.equal(full.cpu().view(torch.int16), want.view(torch.int16))
+            gat.advance()
+        # the prepared-argument plan the benchmark uses
+        plan = sharded.ShardedW8A8LinearPlan(d["x"].to(dev), d["smooth_scales"].to(dev), w.to(dev), sc.to(dev), gat)
+        for _ in range(3):
+            plan.run()
+            full = gat.finish()
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(full.cpu().view(torch.int16), want.view(torch.int16))
+            gat.advance()
+        # collective-fused operators against the oracle of all ranks' inputs (same seed on every rank)
+        g = torch.Generator().manual_seed(5)
+        mm, kk, nn = 128, 256, 256
+        x1l = [workloads.rand_int8((mm, kk), g) for _ in range(world)]
+        wl = [workloads.rand_int8((nn, kk), g) for _ in range(world)]
+        s1l = [workloads.rand_uniform((mm, 1), g, 1e-3, 1e-2) for _ in range(world)]
+        s2l = [workloads.rand_uniform((1, nn), g, 1e-3, 1e-2) for _ in range(world)]
+        hcom = collective_ops.hcom_name()
+        rs_want = oracle.mm_reduce_scatter(x1l, [t.t() for t in wl], s1l, s2l)
+        ar_want = oracle.mm_all_reduce(x1l, [t.t() for t in wl], s2l[0].reshape(-1).to(torch.bfloat16), s1l[0].reshape(-1))
+        ag_want, ag_x1 = oracle.all_gather_mm(x1l, [t.t() for t in wl], s1l, s2l)
+        for _ in range(3):                                # staging buffers alternate between calls
+            rs = pb.npu_mm_reduce_scatter_base(x1l[rank].to(dev), wl[rank].to(dev).t(), hcom, world,
+                                               x1_scale=s1l[rank].to(dev), x2_scale=s2l[rank].to(dev),
+                                               output_dtype=torch.bfloat16, comm_mode="aiv")
+            ar = pb.npu_mm_all_reduce_base(x1l[rank].to(dev), wl[rank].to(dev).t(), hcom, reduce_op="sum",
+                                           dequant_scale=s2l[0].reshape(-1).to(torch.bfloat16).to(dev),
+                                           pertoken_scale=s1l[0].reshape(-1).to(dev))
+            ag, gx = pb.npu_all_gather_base_mm(x1l[rank].to(dev), wl[rank].to(dev).t(), hcom, world,
+                                               x1_scale=s1l[rank].to(dev), x2_scale=s2l[rank].to(dev))
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(rs.cpu().view(torch.int16), rs_want[rank].view(torch.int16))
+            ok = ok and torch.equal(ar.cpu().view(torch.int16), ar_want.view(torch.int16))
+            ok = ok and torch.equal(ag.cpu().view(torch.int16), ag_want[rank].view(torch.int16))
+            ok = ok and torch.equal(gx.cpu(), ag_x1)
+        peers.check()
+        dist.barrier()
         results.put((rank, "ok" if ok else "mismatch"))
+        collective_ops.release_contexts()
         dist.destroy_process_group()
     except Exception as e:                                # pragma: no cover
         results.put((rank, f"fail:{type(e).__name__}:{e}"))
 
 
-def test_two_rank_peer_gather_matches_unsharded_oracle():
+def test_two_rank_peer_gather_and_collective_ops_match_unsharded_oracle():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
+    import queue
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     results = ctx.Queue()
@@ -95,7 +141,21 @@ def test_two_rank_peer_gather_matches_unsharded_oracle():
     procs = [ctx.Process(target=_rank_main, args=(r, 2, port, results)) for r in range(2)]
     for p in procs:
         p.start()
-    out = dict(results.get(timeout=300) for _ in range(2))
-    for p in procs:
-        p.join(timeout=60)
+    out = {}
+    try:
+        for _ in range(2):
+            try:
+                r, msg = results.get(timeout=240)
+            except queue.Empty:
+                break
+            out[r] = msg
+            if msg != "ok":                                # the other rank's barrier will run out; do not wait for it
+                break
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+        for p in procs:                                    # never leave a child (and its kernels) behind
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=10)
     assert out == {0: "ok", 1: "ok"}, out

@@ -156,3 +156,24 @@ def test_trans_quant_param_contract():
     assert p.shape == (1, 4) and p.dtype == torch.int64
     s = torch.tensor([0.0123, 4.5])
     assert np.array_equal(oracle.trans_quant_param_decode(oracle.trans_quant_param(s))[0], s.numpy())
+
+
+def test_reduce_scatter_oracle_matches_reference_golden(golden_dir):
+    """The reference's own TestMmReduceScatterBaseOp._get_global_tensor (test/distributed/tensor/test_matrix_ops.py:86-110)
+    on three ranks of seeded int8 operands: the oracle's rank-ordered fp32 sum must agree to fp32 rounding (the
+    golden multiplies the two scales first, the oracle scales the accumulator one factor at a time)."""
+    ref = np.load(os.path.join(golden_dir, "reference_goldens.npz"))
+    x1 = [torch.from_numpy(a) for a in ref["rs_x1"]]
+    x2 = [torch.from_numpy(a) for a in ref["rs_x2"]]
+    s1 = [torch.from_numpy(a) for a in ref["rs_s1"]]
+    s2 = [torch.from_numpy(a) for a in ref["rs_s2"]]
+    got = torch.cat(oracle.mm_reduce_scatter(x1, x2, s1, s2, output_dtype=torch.float32))
+    want = torch.from_numpy(ref["rs_out"])
+    assert got.shape == want.shape
+    assert torch.allclose(got, want, rtol=4e-7, atol=1e-6)
+    # after the cast the two orders give the same bf16 except where the fp32 value sits on a rounding boundary
+    b = torch.cat(oracle.mm_reduce_scatter(x1, x2, s1, s2, output_dtype=torch.bfloat16))
+    assert oracle.max_mixed_error(b, want.to(torch.bfloat16)) <= 2.0 ** -7
+    # all-reduce form: same sum, replicated
+    ar = oracle.mm_all_reduce(x1, x2, torch.from_numpy(ref["rs_s2"][0]).reshape(-1), output_dtype=torch.float32)
+    assert ar.shape == (6, 32)
