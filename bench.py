@@ -47,8 +47,8 @@ L2_BYTES = 126e6
 # quoted on, from one ncu capture each on a smaller case of the same kernel, as a ratio to that case's
 # algorithmic bytes; the bench scales the ratio to its own launches (traffic grows in proportion with the rows
 # and columns processed).  Sources: profiles/w8a8_umma_pair_kernel_m4096_k8192_n7168.md,
-# profiles/dynamic_quant_staged_m4096_k8192.md.
-NCU_TRAFFIC_RATIO = {"w8a8_umma_pair_kernel": None, "dynamic_quant_staged": None}
+# profiles/dynamic_quant_rows_m4096_k8192.md.
+NCU_TRAFFIC_RATIO = {"w8a8_umma_pair_kernel": None, "dynamic_quant_rows": None}
 
 
 def step_flops():
@@ -429,49 +429,61 @@ def run_b200(args):
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)                # all ranks must agree
         if int(flag.item()) == 0:
             exchange = "nccl_all_gather"
+            peers = None
             gat_gu = sharded.ColumnShardedOutput(M, 2 * FFN, torch.bfloat16, device)
             gat_dn = sharded.ColumnShardedOutput(M, HIDDEN, torch.bfloat16, device)
-        else:
-            plans = (sharded.ShardedW8A8LinearPlan(x, smooth, w_gu, s_gu, gat_gu),
-                     sharded.ShardedW8A8LinearPlan(x_down, smooth_down, w_dn, s_dn, gat_dn))
+    else:
+        gat_gu = sharded.LocalOutput(M, 2 * FFN, torch.bfloat16, device)
+        gat_dn = sharded.LocalOutput(M, HIDDEN, torch.bfloat16, device)
+    if exchange != "nccl_all_gather":
+        plans = (sharded.ShardedW8A8LinearPlan(x, smooth, w_gu, s_gu, gat_gu),
+                 sharded.ShardedW8A8LinearPlan(x_down, smooth_down, w_dn, s_dn, gat_dn))
+        if world > 1:
             nopush = (sharded.ShardedW8A8LinearPlan(x, smooth, w_gu, s_gu, gat_gu, fused_push=False),
                       sharded.ShardedW8A8LinearPlan(x_down, smooth_down, w_dn, s_dn, gat_dn, fused_push=False))
     gemm_events, dq_events = [], []
 
     def step(xi, xdi, record=False):
-        """One pass of the path.  N = 1: the public operators.  N > 1: per projection dynamic quant + one GEMM
-        launch whose epilogue also writes the peers' matrices, then one cross-rank barrier for the step."""
-        e = [ev() for _ in range(6)] if record else None
+        """One pass of the path: both dynamic quantisations, then both GEMMs (the two projections of this
+        configuration take independent inputs, so the order inside the step is free; quantising first keeps the
+        bandwidth-bound kernels away from the write-back of the 470 MB gate/up output).  Four C-ABI calls on
+        prepared argument blocks; at N > 1 each GEMM launch also writes the peers' matrices and one
+        cross-rank barrier ends the step.  (NCCL variant: the public operators plus all_gather.)"""
+        e = [ev() for _ in range(5)] if record else None
         if record: e[0].record()
         if plans is not None:
             plans[0].quant(xi)
             if record: e[1].record()
-            plans[0].matmul()
-            if record: e[2].record()
-            if record: e[3].record()
             plans[1].quant(xdi)
-            if record: e[4].record()
+            if record: e[2].record()
+            plans[0].matmul()
+            if record: e[3].record()
             plans[1].matmul()
-            if record: e[5].record()
-            peers.barrier()
+            if record: e[4].record()
+            if peers is not None:
+                peers.barrier()
             o1, o2 = gat_gu.full, gat_dn.full
             gat_gu.advance(); gat_dn.advance()
         else:
-            q, s = ops.npu_dynamic_quant(xi, smooth_scales=smooth)
-            if record: e[1].record()
-            y1 = ops.npu_quant_matmul(q, w_gu.t(), s_gu, pertoken_scale=s, output_dtype=torch.bfloat16)
-            if record: e[2].record()
-            o1 = gat_gu.gather(y1) if world > 1 else y1
-            if record: e[3].record()
-            q2, s2 = ops.npu_dynamic_quant(xdi, smooth_scales=smooth_down)
-            if record: e[4].record()
-            y2 = ops.npu_quant_matmul(q2, w_dn.t(), s_dn, pertoken_scale=s2, output_dtype=torch.bfloat16)
-            if record: e[5].record()
-            o2 = gat_dn.gather(y2) if world > 1 else y2
+            o1, o2 = step_public(xi, xdi, e)
         if record:
-            dq_events.extend([(e[0], e[1]), (e[3], e[4])])
-            gemm_events.extend([(e[1], e[2]), (e[4], e[5])])
+            dq_events.extend([(e[0], e[1]), (e[1], e[2])])
+            gemm_events.extend([(e[2], e[3]), (e[3], e[4])])
         return o1, o2
+
+    def step_public(xi, xdi, e=None):
+        """The same pass through the public operators torch.ops.npu.* (what a user of the reference calls)."""
+        q, s = ops.npu_dynamic_quant(xi, smooth_scales=smooth)
+        if e: e[1].record()
+        q2, s2 = ops.npu_dynamic_quant(xdi, smooth_scales=smooth_down)
+        if e: e[2].record()
+        y1 = ops.npu_quant_matmul(q, w_gu.t(), s_gu, pertoken_scale=s, output_dtype=torch.bfloat16)
+        if e: e[3].record()
+        y2 = ops.npu_quant_matmul(q2, w_dn.t(), s_dn, pertoken_scale=s2, output_dtype=torch.bfloat16)
+        if e: e[4].record()
+        if world > 1:
+            return gat_gu.gather(y1), gat_dn.gather(y2)
+        return y1, y2
 
     def barrier():
         if world > 1:
@@ -519,7 +531,7 @@ def run_b200(args):
     dq_ms = time_events(dq_events) / len(dq_events)
     dev_err = _cabi.device_error()
     parity_ok = check_parity(rank, world, device, d, outs, _cabi, dist) if not args.no_parity else None
-    if plans is not None:
+    if peers is not None:
         peers.check()
 
     # ---- the same step for at least three seconds: clocks settle under the power cap
@@ -539,7 +551,7 @@ def run_b200(args):
     peaks = measured_peaks()
     peak_i8, peak_src = int8_peak(peaks, ms_total * 1e-3)
     return dict(world=world, rank=rank, device=device, d=d, dist=dist, peers=peers, plans=plans, nopush=nopush,
-                gat=(gat_gu, gat_dn), step=step, barrier=barrier, max_over_ranks=max_over_ranks, x=x, x_down=x_down,
+                gat=(gat_gu, gat_dn), step=step, step_public=step_public, barrier=barrier, max_over_ranks=max_over_ranks, x=x, x_down=x_down,
                 exchange=exchange, clocks=clocks, ms_step=ms_step, ms_total=ms_total, value=value, host_ms_step=host_ms_step,
                 gemm_ms=gemm_ms, dq_ms=dq_ms, dev_err=dev_err, parity_ok=parity_ok, sustained=sustained,
                 gemm_flops_per_launch=gemm_flops_per_launch, dq_bytes_per_launch=dq_bytes_per_launch, peaks=peaks,
@@ -548,39 +560,75 @@ def run_b200(args):
 
 
 def measure_e2e(c, args):
-    """The same step end to end: every step copies the activations from pinned host memory to the device and
-    the outputs back (each rank the column block it computed when N > 1, so that every output byte crosses
-    PCIe once; the whole matrices at N = 1)."""
+    """The same step end to end, as a serving loop would run it: every step copies its activations from pinned
+    host memory to the device and its outputs back (each rank the column block it computed when N > 1, so that
+    every output byte crosses PCIe once; the whole matrices at N = 1).  The three stages run on three streams
+    with two sets of buffers, so that the upload of step i+1, the kernels of step i and the download of step
+    i-1 overlap (PCIe is full duplex); every byte of every step is still copied inside the timed region.  At
+    N = 1 the kernels are launched through the public operators torch.ops.npu.*."""
     world, rank, device = c["world"], c["rank"], c["device"]
     x, x_down = c["x"], c["x_down"]
     hx, hxd = x.cpu().pin_memory(), x_down.cpu().pin_memory()
-    dx, dxd = torch.empty_like(x), torch.empty_like(x_down)
+    dx = [torch.empty_like(x) for _ in range(2)]
+    dxd = [torch.empty_like(x_down) for _ in range(2)]
     n1, n2 = 2 * FFN // world, HIDDEN // world
-    ho1 = torch.empty((M, n1), dtype=torch.bfloat16).pin_memory()
-    ho2 = torch.empty((M, n2), dtype=torch.bfloat16).pin_memory()
+    ho1 = [torch.empty((M, n1), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    ho2 = [torch.empty((M, n2), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)
+    ev_in = [torch.cuda.Event() for _ in range(2)]        # upload of buffer set b has landed
+    ev_used = [torch.cuda.Event() for _ in range(2)]      # the kernels have consumed buffer set b
+    ev_out = [torch.cuda.Event() for _ in range(2)]       # download of the outputs of set b has finished
+    for e_ in ev_used + ev_out:
+        e_.record(main)
+    state = {"i": 0}
 
     def e2e_step():
-        dx.copy_(hx, non_blocking=True)
-        dxd.copy_(hxd, non_blocking=True)
-        o1, o2 = c["step"](dx, dxd)
-        ho1.copy_(o1[:, rank * n1:(rank + 1) * n1], non_blocking=True)
-        ho2.copy_(o2[:, rank * n2:(rank + 1) * n2], non_blocking=True)
+        b = state["i"] % 2
+        state["i"] += 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_used[b])
+            dx[b].copy_(hx, non_blocking=True)
+            dxd[b].copy_(hxd, non_blocking=True)
+            ev_in[b].record(s_in)
+        main.wait_event(ev_in[b])
+        main.wait_event(ev_out[b])                         # the result matrices of two steps ago have been read out
+        if world > 1:
+            # Peers write into this rank's result matrix of step i during their step i+2, which they may start once
+            # this rank has joined the barrier of step i+1: that barrier must not be queued before step i's download.
+            main.wait_event(ev_out[1 - b])
+        o1, o2 = (c["step_public"] if world == 1 else c["step"])(dx[b], dxd[b])
+        ev_used[b].record(main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_used[b])
+            ho1[b].copy_(o1[:, rank * n1:(rank + 1) * n1], non_blocking=True)
+            ho2[b].copy_(o2[:, rank * n2:(rank + 1) * n2], non_blocking=True)
+            ev_out[b].record(s_out)
+        o1.record_stream(s_out)
+        o2.record_stream(s_out)
 
-    e2e_steps = max(3, min(args.steps, 10))
+    def drain():
+        main.wait_stream(s_in)
+        main.wait_stream(s_out)
+
+    e2e_steps = max(4, min(args.steps, 10))
     for _ in range(2):
         e2e_step()
+    drain()
     c["barrier"]()
     t0, t1 = ev(), ev()
     t0.record()
     for _ in range(e2e_steps):
         e2e_step()
+    drain()
     t1.record()
     c["barrier"]()
     e2e_ms = c["max_over_ranks"](t0.elapsed_time(t1)) / e2e_steps
     return {"value": round(step_flops() / (e2e_ms * 1e-3) / 1e12, 2), "unit": UNIT, "ms_per_step": round(e2e_ms, 4),
             "h2d_bytes_per_step": world * (hx.numel() + hxd.numel()) * 2,
-            "d2h_bytes_per_step": world * (ho1.numel() + ho2.numel()) * 2,
-            "note": "every rank copies both activation tensors in (replicated inputs) and its own column blocks out"}
+            "d2h_bytes_per_step": world * (ho1[0].numel() + ho2[0].numel()) * 2,
+            "note": "every rank copies both activation tensors in (replicated inputs) and its own column blocks out; "
+                    "upload, kernels and download of consecutive steps overlap on three streams (two buffer sets)"}
 
 
 def measure_multi_gpu_extras(c, args):
@@ -782,13 +830,13 @@ def run_and_print(args):
     from pytorch_b200 import _cabi
     world, rank = c["world"], c["rank"]
     e2e = measure_e2e(c, args)
-    multi = measure_multi_gpu_extras(c, args) if c["plans"] is not None else {}
+    multi = measure_multi_gpu_extras(c, args) if c["nopush"] is not None else {}
     peaks, peak_i8 = c["peaks"], c["peak_i8"]
     gemm_tops = c["gemm_flops_per_launch"] / (c["gemm_ms"] * 1e-3) / 1e12
     dq_gbs = c["dq_bytes_per_launch"] / (c["dq_ms"] * 1e-3) / 1e9
     gemm_alg_bytes = ((M * HIDDEN + HIDDEN * 2 * FFN / world + M * 2 * FFN / world * 2) +
                       (M * FFN + FFN * HIDDEN / world + M * HIDDEN / world * 2)) / 2
-    tr_g, tr_d = NCU_TRAFFIC_RATIO["w8a8_umma_pair_kernel"], NCU_TRAFFIC_RATIO["dynamic_quant_staged"]
+    tr_g, tr_d = NCU_TRAFFIC_RATIO["w8a8_umma_pair_kernel"], NCU_TRAFFIC_RATIO["dynamic_quant_rows"]
     frac = gemm_tops / peak_i8
     out = {
         "metric": METRIC, "value": round(c["value"], 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -805,7 +853,7 @@ def run_and_print(args):
         "device_error": c["dev_err"],
         "host_launch_ms_per_step": round(c["host_ms_step"], 4),
         "e2e": e2e,
-        "gpu_launches": (4 if world == 1 else 5 if c["plans"] is not None else 4) * args.steps,
+        "gpu_launches": (4 if world == 1 else 5 if c["peers"] is not None else 4) * args.steps,
         "roofline": {"bound": "tensor", "kernel": "w8a8_umma_pair_kernel", "achieved": round(gemm_tops, 1),
                      "peak": round(peak_i8, 1), "unit": "TOP/s", "frac": round(frac, 4),
                      "frac_of_nominal_int8": round(gemm_tops / NOMINAL_INT8_TOPS, 4),
@@ -816,7 +864,7 @@ def run_and_print(args):
                      "avg_launch_ms": round(c["gemm_ms"], 4),
                      "note": "at N > 1 the launch also stores its tiles into the peers' matrices, so its duration "
                              "includes the exchange" if world > 1 else "average of the gate/up and the down launch"},
-        "roofline_dynamic_quant": {"bound": "hbm", "kernel": "dynamic_quant_staged", "achieved": round(dq_gbs, 1),
+        "roofline_dynamic_quant": {"bound": "hbm", "kernel": "dynamic_quant_rows", "achieved": round(dq_gbs, 1),
                                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(dq_gbs / peaks["hbm_gbs"], 4),
                                    "traffic": None if tr_d is None else round(tr_d * c["dq_bytes_per_launch"]),
                                    "algorithmic_bytes": round(c["dq_bytes_per_launch"]),

@@ -11,6 +11,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace b200q {
@@ -47,21 +49,18 @@ __device__ __forceinline__ void st_stream(uint2* p, uint2 v) {
   asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
 
-// Eight consecutive smooth-scale values as fp32 (the vector is re-read by every row and
+// Eight consecutive smooth-scale values as four fp32 pairs (the vector is re-read by every row and
 // stays in L1/L2).
-__device__ __forceinline__ void load_smooth8(const float* p, float (&s)[8]) {
+__device__ __forceinline__ void load_smooth8(const float* p, float2 (&s)[4]) {
   const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-  s[0] = a.x, s[1] = a.y, s[2] = a.z, s[3] = a.w, s[4] = b.x, s[5] = b.y, s[6] = b.z, s[7] = b.w;
+  s[0] = make_float2(a.x, a.y), s[1] = make_float2(a.z, a.w), s[2] = make_float2(b.x, b.y), s[3] = make_float2(b.z, b.w);
 }
 template <typename ST>
-__device__ __forceinline__ void load_smooth8(const ST* p, float (&s)[8]) {
+__device__ __forceinline__ void load_smooth8(const ST* p, float2 (&s)[4]) {
   const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
   const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float2 f = unpack2<ST>(w[j]);
-    s[2 * j] = f.x, s[2 * j + 1] = f.y;
-  }
+  for (int j = 0; j < 4; ++j) s[j] = unpack2<ST>(w[j]);
 }
 
 // Reciprocal of a row's scale for quantize8.  0 for an all-zero row (every product is then 0); NaN marks
@@ -73,32 +72,65 @@ __device__ __forceinline__ float quant_inverse(float scale) {
   return __frcp_rn(scale);
 }
 
-// Eight values -> eight int8 (packed), bit-exact with clamp(rint(xs / scale)).
+// Eight values (four fp32 pairs) -> eight int8 (packed), bit-exact with clamp(rint(xs / scale)).
 // With y = RN(1/scale): q0 = RN(f*y) is within one ulp of the quotient, r = f - q0*scale is exact in one
 // fused multiply-add, and RN(q0 + r*y) is then the correctly rounded IEEE quotient (Markstein's division
 // refinement; it needs y correctly rounded, which __frcp_rn gives, and no overflow or underflow, which
 // quant_inverse rules out).  Adding 1.5 * 2^23 rounds that quotient to the nearest-even integer and leaves its
 // two's-complement low byte in the low mantissa byte; |xs/scale| <= 127.0001 because scale = amax/127,
-// so no clamp is needed.  No branch, no division.
-__device__ __forceinline__ uint2 quantize8(const float (&f)[8], float scale, float inv) {
-  constexpr float kMagic = 12582912.0f;
+// so no clamp is needed.  No branch, no division; the four steps are packed two-wide fp32 instructions
+// (fma.rn.f32x2 and friends of sm_100), each lane rounded exactly like the scalar instruction, which halves
+// the issue slots of a kernel that is bound by instruction issue, not by arithmetic.
+__device__ __forceinline__ uint2 quantize8(const float2 (&f)[4], float scale, float inv) {
   uint32_t u[8];
   if (inv == inv) {
+    const float2 inv2 = make_float2(inv, inv), nscale2 = make_float2(-scale, -scale);
+    const float2 magic2 = make_float2(12582912.0f, 12582912.0f);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float q0 = __fmul_rn(f[j], inv);
-      const float r = __fmaf_rn(-q0, scale, f[j]);
-      const float q = __fmaf_rn(r, inv, q0);
-      u[j] = __float_as_uint(__fadd_rn(q, kMagic));
+    for (int j = 0; j < 4; ++j) {
+      const float2 q0 = __fmul2_rn(f[j], inv2);
+      const float2 r = __ffma2_rn(q0, nscale2, f[j]);
+      const float2 q = __ffma2_rn(r, inv2, q0);
+      const float2 m = __fadd2_rn(q, magic2);
+      u[2 * j] = __float_as_uint(m.x);
+      u[2 * j + 1] = __float_as_uint(m.y);
     }
   } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) u[j] = (uint32_t)__float2int_rn(__fdiv_rn(f[j], scale));
+    for (int j = 0; j < 4; ++j) {
+      u[2 * j] = (uint32_t)__float2int_rn(__fdiv_rn(f[j].x, scale));
+      u[2 * j + 1] = (uint32_t)__float2int_rn(__fdiv_rn(f[j].y, scale));
+    }
   }
   uint2 o;
   o.x = __byte_perm(__byte_perm(u[0], u[1], 0x0040), __byte_perm(u[2], u[3], 0x0040), 0x5410);
   o.y = __byte_perm(__byte_perm(u[4], u[5], 0x0040), __byte_perm(u[6], u[7], 0x0040), 0x5410);
   return o;
+}
+
+// The same for callers that hold eight separate floats.
+__device__ __forceinline__ uint2 quantize8(const float (&f)[8], float scale, float inv) {
+  const float2 g[4] = {{f[0], f[1]}, {f[2], f[3]}, {f[4], f[5]}, {f[6], f[7]}};
+  return quantize8(g, scale, inv);
+}
+template <typename ST>
+__device__ __forceinline__ void load_smooth8(const ST* p, float (&s)[8]) {
+  float2 t[4];
+  load_smooth8(p, t);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) s[2 * j] = t[j].x, s[2 * j + 1] = t[j].y;
+}
+
+// x*smooth for the four pairs of one vector, and the running maximum of their magnitudes.
+template <typename T, bool SMOOTH>
+__device__ __forceinline__ void products8(const uint4& raw, const float2 (&sm)[4], float2 (&f)[4], float& amax) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 pr = unpack2<T>(w[j]);
+    f[j] = SMOOTH ? __fmul2_rn(pr, sm[j]) : pr;
+    amax = fmaxf(amax, fmaxf(fabsf(f[j].x), fabsf(f[j].y)));
+  }
 }
 
 // Maximum of a non-negative value over the CTA.  Non-negative floats order like their bit patterns,
@@ -125,7 +157,7 @@ __global__ void __launch_bounds__(ITERS == 4 ? 1024 : 512) dynamic_quant_rows(co
   __shared__ float red[2][32];
   const int nvec = k >> 3;
   uint4 nxt[ITERS];
-  float f[ITERS][8];
+  float2 f[ITERS][4];
   auto load_row = [&](int64_t row) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * k) + threadIdx.x;
 #pragma unroll
@@ -140,16 +172,9 @@ __global__ void __launch_bounds__(ITERS == 4 ? 1024 : 512) dynamic_quant_rows(co
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
       const int v = threadIdx.x + i * blockDim.x;
-      const uint32_t w[4] = {nxt[i].x, nxt[i].y, nxt[i].z, nxt[i].w};
-      float sm[8];
+      float2 sm[4] = {{1.0f, 1.0f}, {1.0f, 1.0f}, {1.0f, 1.0f}, {1.0f, 1.0f}};     // past the row: 0 * 1
       if (SMOOTH && (FULL || v < nvec)) load_smooth8(smooth + v * 8, sm);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 pr = unpack2<T>(w[j]);
-        f[i][2 * j] = (SMOOTH && (FULL || v < nvec)) ? __fmul_rn(pr.x, sm[2 * j]) : pr.x;
-        f[i][2 * j + 1] = (SMOOTH && (FULL || v < nvec)) ? __fmul_rn(pr.y, sm[2 * j + 1]) : pr.y;
-        amax = fmaxf(amax, fmaxf(fabsf(f[i][2 * j]), fabsf(f[i][2 * j + 1])));
-      }
+      products8<T, SMOOTH>(nxt[i], sm, f[i], amax);
     }
     if (row + gridDim.x < rows) load_row(row + gridDim.x);   // in flight during the reduction and quantisation
     amax = block_max(amax, red[par]);
@@ -161,99 +186,6 @@ __global__ void __launch_bounds__(ITERS == 4 ? 1024 : 512) dynamic_quant_rows(co
     for (int i = 0; i < ITERS; ++i)
       if (FULL || threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8(f[i], scale, inv));
   }
-}
-
-// Staged kernel.  Persistent CTAs stride over the rows; thread 0 keeps `stages` rows in flight with one
-// bulk copy per row into a shared-memory ring, each completing on its own mbarrier.  Per row: wait for the
-// row, pull this thread's ITERS vectors out of shared memory, form the fp32 products x*smooth once and
-// keep them in registers, reduce the row maximum (the __syncthreads inside also tells thread 0 that every
-// thread has finished reading the stage, so it refills it with the row `stages` ahead at once), quantise
-// from registers, stream the int8 out.  x is read from HBM exactly once and never waits on registers.
-template <typename T, typename ST, int ITERS, bool SMOOTH>
-__global__ void __launch_bounds__(512) dynamic_quant_staged(const T* __restrict__ x, const ST* __restrict__ smooth,
-                                                           int8_t* __restrict__ y, float* __restrict__ scale_out,
-                                                           int64_t rows, int k, int stages) {
-  extern __shared__ __align__(128) uint8_t dq_smem[];
-  __shared__ float red[2][32];
-  __shared__ uint64_t full[12];
-  __shared__ int abort_flag;
-  const int nvec = k >> 3;
-  const uint32_t row_bytes = (uint32_t)k * 2u;
-  const uint32_t ring = smem_u32(dq_smem);
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < stages; ++i) mbar_init(&full[i], 1);
-    abort_flag = 0;
-    fence_mbar_init();
-  }
-  __syncthreads();
-  const uint64_t pol = policy_evict_first();
-  auto fetch = [&](int64_t row, int stage) {          // thread 0 only
-    mbar_arrive_expect_tx(&full[stage], row_bytes);
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
-        ::"r"(ring + (uint32_t)stage * row_bytes), "l"(x + row * k), "r"(row_bytes), "r"(smem_u32(&full[stage])), "l"(pol)
-        : "memory");
-  };
-  if (threadIdx.x == 0) {
-    int64_t r = blockIdx.x;
-    for (int i = 0; i < stages && r < rows; ++i, r += gridDim.x) fetch(r, i);
-  }
-  // The smooth scales of this thread's columns are the same for every row: keep them in registers when
-  // they fit (ITERS <= 2), else re-read them (they stay in L1).
-  float smk[ITERS <= 2 ? ITERS : 1][8];
-  if (SMOOTH && ITERS <= 2) {
-#pragma unroll
-    for (int i = 0; i < ITERS; ++i) {
-      const int v = threadIdx.x + i * blockDim.x;
-      if (v < nvec) load_smooth8(smooth + v * 8, smk[i]);
-    }
-  }
-  int stage = 0, par = 0;
-  uint32_t phase = 0;
-  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, par ^= 1) {
-    // A wait that gives up must end the loop for the whole CTA at the same place: the thread contributes a
-    // sentinel above every float to the maximum reduction below, which every thread then sees.
-    const bool got = mbar_wait(&full[stage], phase, &abort_flag, kDevTimeoutProducer);
-    const uint32_t src = ring + (uint32_t)stage * row_bytes + threadIdx.x * 16;
-    float f[ITERS][8];
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < ITERS; ++i) {
-      const int v = threadIdx.x + i * blockDim.x;
-      const bool in = got && v < nvec;
-      const uint4 raw = in ? ld_shared_v4(src + i * blockDim.x * 16) : make_uint4(0, 0, 0, 0);
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-      float sm[8];
-      if (SMOOTH && ITERS > 2 && in) load_smooth8(smooth + v * 8, sm);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 pr = unpack2<T>(w[j]);
-        const float s0 = !SMOOTH ? 1.0f : (ITERS <= 2 ? smk[ITERS <= 2 ? i : 0][2 * j] : sm[2 * j]);
-        const float s1 = !SMOOTH ? 1.0f : (ITERS <= 2 ? smk[ITERS <= 2 ? i : 0][2 * j + 1] : sm[2 * j + 1]);
-        f[i][2 * j] = (SMOOTH && in) ? __fmul_rn(pr.x, s0) : pr.x;
-        f[i][2 * j + 1] = (SMOOTH && in) ? __fmul_rn(pr.y, s1) : pr.y;
-        amax = fmaxf(amax, fmaxf(fabsf(f[i][2 * j]), fabsf(f[i][2 * j + 1])));
-      }
-    }
-    amax = block_max(got ? amax : __uint_as_float(0xFFFFFFFFu), red[par]);   // every thread has read its part of the stage
-    if (__float_as_uint(amax) == 0xFFFFFFFFu) break;
-    if (threadIdx.x == 0) {
-      const int64_t nxt = row + (int64_t)stages * gridDim.x;
-      if (nxt < rows) fetch(nxt, stage);
-    }
-    const float scale = __fdiv_rn(amax, 127.0f);
-    if (threadIdx.x == 0) scale_out[row] = scale;
-    const float inv = quant_inverse(scale);
-    uint2* yr = reinterpret_cast<uint2*>(y + row * k) + threadIdx.x;
-#pragma unroll
-    for (int i = 0; i < ITERS; ++i)
-      if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8(f[i], scale, inv));
-    if (++stage == stages) { stage = 0; phase ^= 1; }
-  }
-  // Copies still in flight when a wait gave up must land before the shared memory is released.
-  if (abort_flag && threadIdx.x == 0)
-    for (int i = 0; i < 200; ++i) __nanosleep(1000);
-  __syncthreads();
 }
 
 // Generic path: any k, any alignment; the row is read twice (second pass from L2).
@@ -293,36 +225,6 @@ int launch_dq(const void* x, const void* smooth, int8_t* y, float* scale, int64_
     return check_launch("dynamic_quant (generic)");
   }
   const int nvec = (int)(k / 8);
-  if (k >= 1024 && k <= 32768) {
-    // Staged kernel: the fewest vectors per thread that keep the CTA at 384 threads or fewer (eight vectors
-    // and up to 512 threads for the longest rows); as many CTAs per SM as 64 KB (rows up to 16 KB), 96 KB
-    // (up to 32 KB) or 200 KB rings allow.
-    int it = 1;
-    while (it < 8 && ceil_div(nvec, it) > (it == 4 ? 512 : 384)) it *= 2;
-    int threads = (int)ceil_div(ceil_div(nvec, it), 32) * 32;
-    const int64_t row_bytes = k * 2;
-    const int64_t budget = row_bytes <= 16384 ? 65536 : row_bytes <= 32768 ? 98304 : 204800;
-    int stages = (int)(budget / row_bytes);
-    stages = stages > 12 ? 12 : stages < 2 ? 2 : stages;
-    const int smem = (int)(stages * row_bytes);
-    int per_sm = 1;
-#define B200Q_DQS_LAUNCH(I)                                                                                    \
-  {                                                                                                            \
-    constexpr auto kern = dynamic_quant_staged<T, ST, I, SMOOTH>;                                             \
-    if (int rc = ensure_dynamic_smem<kern>(204800, "dynamic_quant")) return rc;                               \
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem);                               \
-    const int64_t cap = (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);                                       \
-    kern<<<(unsigned)(rows < cap ? rows : cap), threads, smem, st>>>(xp, sp, y, scale, rows, (int)k, stages); \
-  }
-    switch (it) {
-      case 1: B200Q_DQS_LAUNCH(1) break;
-      case 2: B200Q_DQS_LAUNCH(2) break;
-      case 4: B200Q_DQS_LAUNCH(4) break;
-      default: B200Q_DQS_LAUNCH(8) break;
-    }
-#undef B200Q_DQS_LAUNCH
-    return check_launch("dynamic_quant (staged)");
-  }
   // Up to four 128-bit loads per thread (32 fp32 products kept in registers) with <= 256 threads where
   // the row allows it (k <= 8192); longer rows widen the CTA up to 1024 threads (k <= 32768), then take
   // 8 and 16 loads per thread with 512 threads.
@@ -330,6 +232,10 @@ int launch_dq(const void* x, const void* smooth, int8_t* y, float* scale, int64_
   while (iters < 4 && nvec > iters * 256) iters *= 2;
   if (nvec > 4 * 1024)                                   // k > 32768: more loads per thread
     while (iters < 16 && nvec > iters * 512) iters *= 2;
+  if (const char* env = getenv("B200Q_DQ_ITERS")) {       // tuning aid: force the loads per thread
+    const int v = atoi(env);
+    if ((v == 1 || v == 2 || v == 4 || v == 8 || v == 16) && ceil_div(nvec, v) <= (v == 4 ? 1024 : 512)) iters = v;
+  }
   int threads = (int)ceil_div(nvec, iters);
   threads = (int)ceil_div(threads, 32) * 32;
   const bool full = (int64_t)threads * iters == nvec;

@@ -1061,7 +1061,9 @@ Plan make_plan(int64_t m, int64_t k, int64_t n, int64_t sk, int64_t sn, const vo
       const double cost = (double)ceil_div(tiles, clusters) * (double)per + 0.5 * c;
       if (cost < best) { best = cost; p.csize = c; }
     }
-    p.decode = tiles * p.csize * 2 >= sms;                // at least half of the SMs get work
+    // Measured: the cluster kernel wins where one round of resident clusters covers all channel tiles and the
+    // token tile is the smallest (per-tile synchronisation across the cluster is not hidden otherwise).
+    p.decode = m <= 16 && tiles <= sms / p.csize && tiles * p.csize * 2 >= sms;
     const char* env = getenv("B200Q_W8A8_DECODE");
     if (env) p.decode = env[0] != '0';
     if (!p.decode) {
@@ -1084,7 +1086,10 @@ Plan make_plan(int64_t m, int64_t k, int64_t n, int64_t sk, int64_t sn, const vo
     p.bn = n <= 128 ? 128 : 256;
     // CTA pairs (256 x 256 tiles, one per two SMs) against single CTAs (128 x BN tiles): both give an SM
     // the same work per tile, the pair streams a third less into shared memory and runs about a tenth
-    // faster, so it wins whenever it does not need more rounds.
+    // faster, so it wins whenever it does not need more rounds.  (A stream-K schedule for tile counts that
+    // do not fill the last round - equal K-block ranges per pair, int32 partial tiles through scratch - was
+    // built and measured 25-65 % SLOWER on every such shape: the pairs then sit at different K offsets, and
+    // the kernel depends on concurrently running pairs fetching the same operand tiles at the same time.)
     const char* env = getenv("B200Q_W8A8_PAIR");
     const bool allow = env ? (env[0] != '0') : true;
     const int64_t t_pair = ceil_div(m, 256) * ceil_div(n, 256), t_one = ceil_div(m, kTileA) * ceil_div(n, p.bn);

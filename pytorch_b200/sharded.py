@@ -168,6 +168,35 @@ class PeerColumnGather:
         return self.finish()
 
 
+class LocalOutput:
+    """The single-GPU stand-in for :class:`PeerColumnGather`: plain ``[M, N]`` result matrices, no peers, so
+    that :class:`ShardedW8A8LinearPlan` can drive an unsharded linear through the same prepared C-ABI calls."""
+
+    def __init__(self, m: int, n: int, dtype: torch.dtype, device, buffers: int = 2):
+        self.world, self.rank, self.m, self.n, self.lo, self.hi = 1, 0, m, n, 0, n
+        self.bufs = [(torch.empty((m, n), dtype=dtype, device=device), [], None) for _ in range(buffers)]
+        self.cur = 0
+
+    @property
+    def full(self) -> torch.Tensor:
+        return self.bufs[self.cur][0]
+
+    def advance(self) -> None:
+        self.cur = (self.cur + 1) % len(self.bufs)
+
+    def local_block(self) -> torch.Tensor:
+        return self.full
+
+    def peer_blocks(self):
+        return []
+
+    def push(self) -> None:
+        pass
+
+    def finish(self) -> torch.Tensor:
+        return self.full
+
+
 class ShardedW8A8LinearPlan:
     """One column-sharded W8A8 linear with every buffer and C-ABI argument block prepared once:
     dynamic quant of ``x`` (replicated), then one GEMM launch that writes this rank's columns into the
