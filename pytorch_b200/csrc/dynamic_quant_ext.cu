@@ -51,20 +51,34 @@ __device__ __forceinline__ int quant_asym_exact(float f, float scale, float offs
   return max(-128, min(127, q));
 }
 
+// Eight values -> eight int8, bit-exact with clamp(rint(xs / scale + offset)): the correctly rounded quotient by
+// the same two-FMA refinement as the symmetric kernel (quantize8), one rounded addition of the offset, then the
+// 1.5 * 2^23 addition that rounds to the nearest-even integer and leaves its low byte in the mantissa.  The
+// result lies in [-128, 127] by construction (offset = 127 - max/scale, scale = (max - min)/255) as long as the
+// offset is moderate, which the caller checks, so no clamp.
+// Packed two-wide fp32 instructions; a constant row (scale 0) gives 0, a scale too small for a finite
+// reciprocal (inv is NaN) takes true divisions.
 __device__ __forceinline__ uint2 quantize8_asym(const float (&f)[8], float scale, float inv, float offset) {
-  constexpr float kMagic = 12582912.0f;
   uint32_t u[8];
-  float dist = 0.0f;
+  if (scale == 0.0f) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float t = __fmaf_rn(f[j], inv, offset);
-    const float uf = __fadd_rn(t, kMagic);
-    dist = fmaxf(dist, fabsf(__fsub_rn(t, __fsub_rn(uf, kMagic))));
-    u[j] = __float_as_uint(uf);
-  }
-  if (dist > 0.4999f || scale == 0.0f || !(inv < 3.0e38f)) {   // tiny scale: 1/scale overflowed
+    for (int j = 0; j < 8; ++j) u[j] = 0u;
+  } else if (inv == inv) {
+    const float2 inv2 = make_float2(inv, inv), nscale2 = make_float2(-scale, -scale), off2 = make_float2(offset, offset);
+    const float2 magic2 = make_float2(12582912.0f, 12582912.0f);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) u[j] = scale == 0.0f ? 0u : (uint32_t)quant_asym_exact(f[j], scale, offset);
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = make_float2(f[2 * j], f[2 * j + 1]);
+      const float2 q0 = __fmul2_rn(x, inv2);
+      const float2 r = __ffma2_rn(q0, nscale2, x);
+      const float2 q = __ffma2_rn(r, inv2, q0);
+      const float2 m = __fadd2_rn(__fadd2_rn(q, off2), magic2);
+      u[2 * j] = __float_as_uint(m.x);
+      u[2 * j + 1] = __float_as_uint(m.y);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) u[j] = (uint32_t)quant_asym_exact(f[j], scale, offset);
   }
   return pack8_low_bytes(u);
 }
@@ -121,7 +135,9 @@ dynamic_quant_ext_rows(const T* __restrict__ x, const ST* __restrict__ smooth, c
       const float scale = __fdiv_rn(__fsub_rn(mx, mn), 255.0f);
       const float offset = scale == 0.0f ? 0.0f : __fsub_rn(127.0f, __fdiv_rn(mx, scale));
       if (threadIdx.x == 0) { scale_out[row] = scale; offset_out[row] = offset; }
-      const float inv = scale == 0.0f ? 0.0f : __frcp_rn(scale);
+      // A row whose values sit far from zero compared with their spread has a huge offset; the sum with the
+      // offset then rounds coarsely and can leave [-128, 127], which only the clamping path handles.
+      const float inv = fabsf(offset) < 30000.0f ? quant_inverse(scale) : __int_as_float(0x7fc00000);
 #pragma unroll
       for (int i = 0; i < ITERS; ++i)
         if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8_asym(f[i], scale, inv, offset));

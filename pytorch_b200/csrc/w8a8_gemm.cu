@@ -679,10 +679,11 @@ w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 // Decode shapes (M <= 128) in one launch: swapped operands as above (weight rows on the 128-row MMA axis,
 // tokens padded to BN), and K split across the CTAs of a thread-block cluster instead of across
 // independent CTAs.  Each CTA of a cluster accumulates its K range of the same 128-channel tile in its
-// own TMEM; the non-leader CTAs then park their int32 partial tile in their shared memory, the leader
-// adds them through distributed shared memory (coalesced ld.shared::cluster, lanes = channels) and runs
-// the dequantising epilogue.  No scratch in global memory, no atomics, no second kernel.  Clusters are
-// persistent and stride over the channel tiles.
+// own TMEM and parks the int32 partial tile in its shared memory; then every CTA finishes its share of the
+// token columns: it adds all CTAs' partial tiles for those columns through distributed shared memory
+// (coalesced ld.shared::cluster, lanes = channels) and runs the dequantising epilogue, so reduction and
+// epilogue are spread over the cluster.  No scratch in global memory, no atomics, no second kernel.
+// Clusters are persistent and stride over the channel tiles.
 template <int BN, int STAGES>
 struct DecodeLayout {
   static constexpr int kBTileBytes = BN * kBK;
@@ -714,11 +715,10 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
-  uint64_t* red_ready = tempty + 2;     // leader: every other CTA of the cluster has parked its partial tile
-  uint64_t* red_free = red_ready + 1;   // others: the leader has read this CTA's partial tile
+  uint64_t* red_ready = tempty + 2;     // every CTA of the cluster has parked its partial tile
+  uint64_t* red_free = red_ready + 1;   // every CTA of the cluster has finished reading this CTA's partial tile
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
-  float* col_pt = reinterpret_cast<float*>(smem + L::kColOff);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t crank = cluster_ctarank(), csize = cluster_nctarank();
@@ -735,8 +735,8 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       mbar_init(&tfull[i], 1);
       mbar_init(&tempty[i], kEpiThreads / 32);
     }
-    mbar_init(red_ready, csize > 1 ? csize - 1 : 1);
-    mbar_init(red_free, 1);
+    mbar_init(red_ready, csize);       // one arrival per CTA of the cluster, this one included
+    mbar_init(red_free, csize);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tensormap(&tmA);
@@ -808,20 +808,41 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint32_t tphase = 0, rphase = 0;
     for (int u = cluster; u < s.units; u += nclusters) {
       const int ta = u % s.tiles_a, tb = u / s.tiles_a;
-      if (crank == 0) {
-        named_barrier_sync(1, kEpiThreads);
-        for (int i = et; i < BN; i += kEpiThreads) {
-          const int64_t mm = (int64_t)tb * BN + i;
-          col_pt[i] = ((e.flags & kHasPt) && mm < e.m) ? __ldg(e.pertoken + mm) : 1.0f;
-        }
-        named_barrier_sync(1, kEpiThreads);
-      }
+      const int64_t n = (int64_t)ta * kTileA + row_in_tile;
+      const bool nv = n < e.n;
+      const float sc = nv ? load_scale(e, n) : 0.0f, off = nv ? load_offset(e, n) : 0.0f;
+      const float fb = nv ? load_float_bias(e, n) : 0.0f;
+      const int ib = nv ? load_int_bias(e, n) : 0;
       if (!epilogue_all(mbar_wait(&tfull[buf], tphase, abort_flag, kDevTimeoutEpilogue))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
-      if (crank != 0) {
-        // Park the partial tile: red[col][row], lanes write consecutive words.
-        if (!epilogue_all(mbar_wait(red_free, rphase ^ 1, abort_flag, kDevTimeoutEpilogue))) break;
+      if (csize == 1) {
+        // No split: accumulator -> epilogue.
+#pragma unroll 1
+        for (int c = 0; c < BN / CH; ++c) {
+          uint32_t r[CH];
+          __syncwarp();
+          tmem_ld_chunk<CH>(taddr + c * CH, r);
+          tmem_ld_wait();
+          if (nv) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int64_t mm = (int64_t)tb * BN + c * CH + j;
+              if (mm < e.m) {
+                const int acc = (int)r[j];
+                const float pt = (e.flags & kHasPt) ? __ldg(e.pertoken + mm) : 1.0f;
+                store_one(e, mm * e.ldo + n, acc, ib, dequant(acc, ib, sc, pt, fb, off, e.flags));
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[buf]);
+      } else {
+        // Every CTA parks its partial tile (red[col][row], lanes write consecutive words) once all CTAs have
+        // finished with the previous one, frees its accumulator, and tells every CTA of the cluster.
+        if (!epilogue_all(mbar_wait_cluster(red_free, rphase ^ 1, abort_flag, kDevTimeoutEpilogue))) break;
 #pragma unroll 1
         for (int c = 0; c < BN / CH; ++c) {
           uint32_t r[CH];
@@ -831,49 +852,44 @@ w8a8_decode_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
           for (int j = 0; j < CH; ++j) red[(c * CH + j) * 128 + row_in_tile] = (int32_t)r[j];
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[buf]);
         fence_acq_rel_cluster();
         named_barrier_sync(1, kEpiThreads);
-        if (et == 0) mbar_arrive_cluster(map_to_cta(smem_u32(red_ready), 0));
-        rphase ^= 1;
-      } else {
-        if (csize > 1 && !epilogue_all(mbar_wait_cluster(red_ready, rphase, abort_flag, kDevTimeoutEpilogue))) break;
-        rphase ^= 1;
-        const int64_t n = (int64_t)ta * kTileA + row_in_tile;
-        const bool nv = n < e.n;
-        const float sc = nv ? load_scale(e, n) : 0.0f, off = nv ? load_offset(e, n) : 0.0f;
-        const float fb = nv ? load_float_bias(e, n) : 0.0f;
-        const int ib = nv ? load_int_bias(e, n) : 0;
+        if (et < (int)csize) mbar_arrive_cluster(map_to_cta(smem_u32(red_ready), (uint32_t)et));
+        if (!epilogue_all(mbar_wait_cluster(red_ready, rphase, abort_flag, kDevTimeoutEpilogue))) break;
+        // This CTA finishes the token columns [crank * per, (crank + 1) * per): the sum over all CTAs' partial
+        // tiles through distributed shared memory (coalesced: lanes = channels), then the epilogue.
+        const int per = BN / (int)csize;
         const uint32_t red_addr = smem_u32(red) + row_in_tile * 4;
 #pragma unroll 1
-        for (int c = 0; c < BN / CH; ++c) {
-          uint32_t r[CH];
-          __syncwarp();
-          tmem_ld_chunk<CH>(taddr + c * CH, r);
-          tmem_ld_wait();
-          for (uint32_t p = 1; p < csize; ++p) {
-            const uint32_t base = map_to_cta(red_addr + (uint32_t)(c * CH) * 512u, p);
+        for (int j0 = 0; j0 < per; j0 += 8) {
+          uint32_t v[8];
 #pragma unroll
-            for (int j = 0; j < CH; ++j) r[j] += ld_shared_cluster_u32(base + j * 512);
+          for (int j = 0; j < 8; ++j) v[j] = 0;
+          for (uint32_t p = 0; p < csize; ++p) {
+            const uint32_t base = map_to_cta(red_addr + (uint32_t)((int)crank * per + j0) * 512u, p);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (j0 + j < per) v[j] += ld_shared_cluster_u32(base + j * 512);
           }
           if (nv) {
 #pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              const int64_t mm = (int64_t)tb * BN + c * CH + j;
-              if (mm < e.m) {
-                const int acc = (int)r[j];
-                store_one(e, mm * e.ldo + n, acc, ib, dequant(acc, ib, sc, col_pt[c * CH + j], fb, off, e.flags));
+            for (int j = 0; j < 8; ++j) {
+              const int64_t mm = (int64_t)tb * BN + (int)crank * per + j0 + j;
+              if (j0 + j < per && mm < e.m) {
+                const int acc = (int)v[j];
+                const float pt = (e.flags & kHasPt) ? __ldg(e.pertoken + mm) : 1.0f;
+                store_one(e, mm * e.ldo + n, acc, ib, dequant(acc, ib, sc, pt, fb, off, e.flags));
               }
             }
           }
         }
-        if (csize > 1) {
-          named_barrier_sync(1, kEpiThreads);         // every thread has finished reading the peers' tiles
-          if (et > 0 && et < (int)csize) mbar_arrive_cluster(map_to_cta(smem_u32(red_free), (uint32_t)et));
-        }
+        named_barrier_sync(1, kEpiThreads);             // every thread of this CTA has finished reading
+        if (et < (int)csize) mbar_arrive_cluster(map_to_cta(smem_u32(red_free), (uint32_t)et));
+        rphase ^= 1;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[buf]);
       if (++buf == 2) { buf = 0; tphase ^= 1; }
     }
   }
@@ -915,6 +931,186 @@ __global__ void w8a8_simt_kernel(const int8_t* __restrict__ x1, const int8_t* __
   const float pt = (e.flags & kHasPt) ? __ldg(e.pertoken + mm) : 1.0f;
   store_one(e, mm * e.ldo + n, acc, ib,
             dequant(acc, ib, load_scale(e, n), pt, load_float_bias(e, n), load_offset(e, n), e.flags));
+}
+
+// One or two tokens (the kernel itself takes up to four): no tensor cores, no pipeline to fill.  A warp streams the K-major weight rows of MT
+// consecutive output channels with 128-bit loads (L1 bypassed, eight loads in flight per lane) against the
+// tokens held in shared memory; a token chunk read from shared memory is used for all MT channels, so the
+// shared-memory traffic per weight byte does not grow with the token count.  Four dp4a per 16 bytes, token
+// and channel, a shuffle reduction, and the lanes 0..MT-1 run the same dequantising epilogue.  The call is
+// one launch whose fixed cost is a plain kernel's, which is what matters when the whole weight streams in a
+// few microseconds.
+template <int MT>
+__global__ void __launch_bounds__(256) w8a8_gemv_kernel(const int8_t* __restrict__ x1, const int8_t* __restrict__ w,
+                                                        int64_t k, int64_t w_pitch, const Epi e) {
+  constexpr int R = MT;                                        // channels per warp and trip
+  constexpr int U = 8 / R;                                     // chunks in flight per channel
+  extern __shared__ __align__(16) uint8_t gemv_x[];           // [MT][k]
+  const int chunks = (int)(k >> 4);                            // 16-byte chunks per row
+  for (int i = threadIdx.x; i < MT * chunks; i += blockDim.x) {
+    const int t = i / chunks, c = i - t * chunks;
+    reinterpret_cast<uint4*>(gemv_x)[i] =
+        t < e.m ? __ldg(reinterpret_cast<const uint4*>(x1 + (int64_t)t * k) + c) : make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t n0 = warp * R; n0 < e.n; n0 += nwarps * R) {
+    int acc[R][MT];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int t = 0; t < MT; ++t) acc[r][t] = 0;
+    for (int c0 = lane; c0 < chunks; c0 += 32 * U) {
+      uint4 v[R][U];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int64_t n = n0 + r < e.n ? n0 + r : e.n - 1;    // past the end: re-read the last row, result unused
+        const uint4* wr = reinterpret_cast<const uint4*>(w + n * w_pitch);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int c = c0 + 32 * u;
+          v[r][u] = make_uint4(0, 0, 0, 0);
+          if (c < chunks)
+            asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(v[r][u].x), "=r"(v[r][u].y), "=r"(v[r][u].z), "=r"(v[r][u].w) : "l"(wr + c));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int c = c0 + 32 * u;
+        if (c < chunks) {
+#pragma unroll
+          for (int t = 0; t < MT; ++t) {
+            const uint4 xv = reinterpret_cast<const uint4*>(gemv_x)[t * chunks + c];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              acc[r][t] = __dp4a((int)v[r][u].x, (int)xv.x, acc[r][t]);
+              acc[r][t] = __dp4a((int)v[r][u].y, (int)xv.y, acc[r][t]);
+              acc[r][t] = __dp4a((int)v[r][u].z, (int)xv.z, acc[r][t]);
+              acc[r][t] = __dp4a((int)v[r][u].w, (int)xv.w, acc[r][t]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[r][t] += __shfl_xor_sync(0xffffffffu, acc[r][t], o);
+      }
+    // lane r finishes channel n0 + r
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (lane == r && n0 + r < e.n) {
+        const int64_t n = n0 + r;
+        const float sc = load_scale(e, n), off = load_offset(e, n), fb = load_float_bias(e, n);
+        const int ib = load_int_bias(e, n);
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+          if (t < e.m) {
+            const float pt = (e.flags & kHasPt) ? __ldg(e.pertoken + t) : 1.0f;
+            store_one(e, (int64_t)t * e.ldo + n, acc[r][t], ib, dequant(acc[r][t], ib, sc, pt, fb, off, e.flags));
+          }
+        }
+      }
+    }
+  }
+}
+
+// Three to sixteen tokens: still bound by the weight stream and too short to fill a tcgen05 pipeline, so the
+// warp-level int8 MMA does the arithmetic (mma.sync m16n8k32: 16 channels x 8 tokens x 32 k per instruction).
+// A CTA of eight warps owns 16 output channels; warp w takes the 64-byte K blocks w, w+8, w+16, ... of those
+// 16 weight rows (so the eight warps together read 512 contiguous bytes of every row), eight or sixteen 128-bit
+// weight loads in flight per lane (the deeper variant, which costs a resident CTA per SM, where there are
+// few CTAs per SM anyway), the tokens' bytes through L1 (the whole activation is a few tens of KB).  Lane
+// (g, q) loads 16 consecutive k of weight rows g and g+8 and of token g: those 16 bytes feed two MMAs whose k
+// slots are a fixed permutation of the 64-wide block, the same permutation for both operands, so no shuffling
+// is needed.  The eight warps' partial sums meet in shared memory and each thread finishes one output element
+// with the common epilogue.  One launch, no scratch.
+__device__ __forceinline__ void mma_s8_16x8x32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NG, int U>   // NG groups of eight tokens: 1 (m <= 8) or 2 (m <= 16); 2 * U weight loads in flight per lane
+__global__ void __launch_bounds__(256) w8a8_small_m_kernel(const int8_t* __restrict__ x1, const int8_t* __restrict__ w,
+                                                           int64_t k, int64_t w_pitch, const Epi e) {
+  __shared__ int red[8][NG * 4][32];
+  const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
+  const int g = lane >> 2, q = lane & 3;
+  const int64_t n0 = (int64_t)blockIdx.x * 16;
+  const int64_t r0 = n0 + g < e.n ? n0 + g : e.n - 1, r1 = n0 + g + 8 < e.n ? n0 + g + 8 : e.n - 1;   // clamped: unused results
+  const int8_t* w0p = w + r0 * w_pitch + q * 16;
+  const int8_t* w1p = w + r1 * w_pitch + q * 16;
+  const int8_t* xp[NG];
+  bool xv[NG];
+#pragma unroll
+  for (int t = 0; t < NG; ++t) {
+    xv[t] = t * 8 + g < e.m;
+    xp[t] = x1 + (int64_t)(xv[t] ? t * 8 + g : 0) * k + q * 16;
+  }
+  int acc[NG][4];
+#pragma unroll
+  for (int t = 0; t < NG; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[t][i] = 0;
+  const int steps = (int)((k + 63) >> 6);
+  for (int s0 = wi; s0 < steps; s0 += 8 * U) {
+    uint4 a[U], b[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t kp = (int64_t)(s0 + 8 * u) * 64;
+      a[u] = b[u] = make_uint4(0, 0, 0, 0);
+      if (kp + q * 16 < k) {
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(a[u].x), "=r"(a[u].y), "=r"(a[u].z), "=r"(a[u].w) : "l"(w0p + kp));
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b[u].x), "=r"(b[u].y), "=r"(b[u].z), "=r"(b[u].w) : "l"(w1p + kp));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t kp = (int64_t)(s0 + 8 * u) * 64;
+      if (kp < k) {                                       // same decision in every lane: the MMA is warp-wide
+#pragma unroll
+        for (int t = 0; t < NG; ++t) {
+          uint4 xr = make_uint4(0, 0, 0, 0);
+          if (xv[t] && kp + q * 16 < k) xr = __ldg(reinterpret_cast<const uint4*>(xp[t] + kp));
+          mma_s8_16x8x32(acc[t], a[u].x, b[u].x, a[u].y, b[u].y, xr.x, xr.y);
+          mma_s8_16x8x32(acc[t], a[u].z, b[u].z, a[u].w, b[u].w, xr.z, xr.w);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < NG; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) red[wi][t * 4 + i][lane] = acc[t][i];
+  __syncthreads();
+  // Thread (reg, lane) finishes one output: accumulator register reg = 4 * token group + i of lane (g, q) is
+  // channel n0 + g + 8 * (i >> 1), token 8 * group + 2 * q + (i & 1).
+  for (int idx = threadIdx.x; idx < NG * 4 * 32; idx += blockDim.x) {
+    const int reg = idx >> 5, ln = idx & 31;
+    int sum = 0;
+#pragma unroll
+    for (int v = 0; v < 8; ++v) sum += red[v][reg][ln];
+    const int i = reg & 3, t = reg >> 2;
+    const int64_t n = n0 + (ln >> 2) + 8 * (i >> 1);
+    const int64_t mm = t * 8 + 2 * (ln & 3) + (i & 1);
+    if (n < e.n && mm < e.m) {
+      const int ib = load_int_bias(e, n);
+      const float pt = (e.flags & kHasPt) ? __ldg(e.pertoken + mm) : 1.0f;
+      store_one(e, mm * e.ldo + n, sum, ib,
+                dequant(sum, ib, load_scale(e, n), pt, load_float_bias(e, n), load_offset(e, n), e.flags));
+    }
+  }
 }
 
 // int8 [k,n] row-major -> [n,k] row-major through a 64x64 shared tile (k, n multiples of 16).
@@ -1025,6 +1221,8 @@ struct Plan {
   bool transpose;       // contiguous [k,n] weight must be re-laid out as [n,k] first
   bool swap;            // M <= 128: weight rows on the MMA's 128-row axis
   bool decode;          // swapped, K split across the CTAs of a cluster (one launch, no scratch)
+  bool gemv;            // one or two tokens: a warp per channel, dp4a, no tensor cores (one launch, no scratch)
+  bool small_m;         // 3..16 tokens: warp-level int8 MMA on a streamed weight (one launch, no scratch)
   bool pair;            // CTA-pair kernel (256 x 256 tiles)
   int bn;               // B-operand tile rows
   int splits;           // swapped without clusters: K split across independent CTAs (int32 scratch + atomics)
@@ -1048,6 +1246,16 @@ Plan make_plan(int64_t m, int64_t k, int64_t n, int64_t sk, int64_t sn, const vo
   p.splits = 1;
   p.csize = 1;
   const int sms = sm_count();
+  if (p.swap && m <= 2 && k * 2 <= 200 * 1024) {
+    const char* env = getenv("B200Q_W8A8_GEMV");
+    p.gemv = env ? (env[0] != '0') : true;
+  }
+  if (p.gemv) return p;
+  if (p.swap && m <= 16) {
+    const char* env = getenv("B200Q_W8A8_SMALL_M");
+    p.small_m = env ? (env[0] != '0') : true;
+  }
+  if (p.small_m) return p;
   if (p.swap) {
     p.bn = m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128;
     const int64_t tiles = ceil_div(n, kTileA), kblocks = ceil_div(k, kBK);
@@ -1061,9 +1269,9 @@ Plan make_plan(int64_t m, int64_t k, int64_t n, int64_t sk, int64_t sn, const vo
       const double cost = (double)ceil_div(tiles, clusters) * (double)per + 0.5 * c;
       if (cost < best) { best = cost; p.csize = c; }
     }
-    // Measured: the cluster kernel wins where one round of resident clusters covers all channel tiles and the
-    // token tile is the smallest (per-tile synchronisation across the cluster is not hidden otherwise).
-    p.decode = m <= 16 && tiles <= sms / p.csize && tiles * p.csize * 2 >= sms;
+    // Measured: the cluster kernel wins where one round of resident clusters covers all channel tiles (the
+    // synchronisation across the cluster at the end of every tile is not hidden when a cluster runs several).
+    p.decode = tiles <= sms / p.csize && tiles * p.csize * 2 >= sms;
     const char* env = getenv("B200Q_W8A8_DECODE");
     if (env) p.decode = env[0] != '0';
     if (!p.decode) {
@@ -1195,6 +1403,42 @@ extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream
     e.acc_ws = reinterpret_cast<int32_t*>(ws + p.ws_transpose);
     cudaError_t err = cudaMemsetAsync(e.acc_ws, 0, (size_t)a->m * a->n * 4, st);
     if (err != cudaSuccess) return fail(B200Q_ERR_LAUNCH, "quant_matmul: memset: %s", cudaGetErrorString(err));
+  }
+
+  if (p.gemv) {
+    const int mt = a->m <= 1 ? 1 : a->m <= 2 ? 2 : 4;
+    const int smem = (int)(mt * a->k);
+    const int64_t want = ceil_div(a->n, 8 * mt);                // 8 warps per CTA, mt channels each per trip
+    const int grid = (int)(want < (int64_t)sm_count() * 8 ? want : (int64_t)sm_count() * 8);
+    int rc = B200Q_OK;
+    switch (mt) {
+      case 1:
+        if ((rc = ensure_dynamic_smem<w8a8_gemv_kernel<1>>(200 * 1024, "quant_matmul"))) return rc;
+        w8a8_gemv_kernel<1><<<grid, 256, smem, st>>>(a->x1, w_nk, a->k, w_pitch, e);
+        break;
+      case 2:
+        if ((rc = ensure_dynamic_smem<w8a8_gemv_kernel<2>>(200 * 1024, "quant_matmul"))) return rc;
+        w8a8_gemv_kernel<2><<<grid, 256, smem, st>>>(a->x1, w_nk, a->k, w_pitch, e);
+        break;
+      default:
+        if ((rc = ensure_dynamic_smem<w8a8_gemv_kernel<4>>(200 * 1024, "quant_matmul"))) return rc;
+        w8a8_gemv_kernel<4><<<grid, 256, smem, st>>>(a->x1, w_nk, a->k, w_pitch, e);
+        break;
+    }
+    return check_launch("quant_matmul (gemv)");
+  }
+
+  if (p.small_m) {
+    const unsigned grid = (unsigned)ceil_div(a->n, 16);
+    const bool deep = (int64_t)grid <= 2 * (int64_t)sm_count();      // measured: 16 loads in flight win below ~2 CTAs per SM
+    if (a->m <= 8) {
+      if (deep) w8a8_small_m_kernel<1, 8><<<grid, 256, 0, st>>>(a->x1, w_nk, a->k, w_pitch, e);
+      else w8a8_small_m_kernel<1, 4><<<grid, 256, 0, st>>>(a->x1, w_nk, a->k, w_pitch, e);
+    } else {
+      if (deep) w8a8_small_m_kernel<2, 8><<<grid, 256, 0, st>>>(a->x1, w_nk, a->k, w_pitch, e);
+      else w8a8_small_m_kernel<2, 4><<<grid, 256, 0, st>>>(a->x1, w_nk, a->k, w_pitch, e);
+    }
+    return check_launch("quant_matmul (warp MMA, few tokens)");
   }
 
   // A operand fills the 128-row MMA axis: tokens normally, channels when swapped.

@@ -280,12 +280,14 @@ def test_dynamic_quant_tiny_rows_keep_ieee_division(cabi):
 
 
 @pytest.mark.parametrize("m,k,n", [(1, 4096, 4096), (16, 8192, 2048), (7, 1024, 9472), (16, 11008, 4096),
-                                   (1, 512, 9600), (128, 1024, 22016), (64, 11008, 4096), (100, 2048, 12288)])
+                                   (3, 11008, 9600), (128, 1024, 22016), (64, 11008, 4096), (100, 2048, 12288)])
 def test_quant_matmul_decode_cluster_split_k(cabi, m, k, n):
-    """Up to 16 tokens against enough channel tiles for one round of clusters: one launch, K split over a
-    thread-block cluster (sizes 4, 8, 2, 4 and 1 for the first five shapes), partial tiles added through
-    distributed shared memory, no scratch.  The last three shapes take the other small-M path (K split over
-    independent CTAs).  int32 accumulators in full and the fused epilogue must match the oracle exactly."""
+    """The paths for few tokens.  By default: one or two tokens a warp per channel (first shape), three to sixteen
+    tokens the warp-MMA streaming kernel (second to fifth shape), both one launch without scratch;
+    more tokens the swapped tcgen05 kernel with K split over independent CTAs.  Then, forced by the library's
+    tuning switches, every shape through the cluster split-K kernel (partial tiles added through distributed
+    shared memory; cluster sizes 1..8, token tiles 16..128, several rounds per cluster) and through the
+    independent-CTA split.  int32 accumulators in full and the fused epilogue must match the oracle exactly."""
     g = torch.Generator().manual_seed(m + k + n)
     x1 = workloads.rand_int8((m, k), g, -128, 127)
     w = workloads.rand_int8((n, k), g, -128, 127)
@@ -301,6 +303,22 @@ def test_quant_matmul_decode_cluster_split_k(cabi, m, k, n):
     for _ in range(3):                                          # persistent clusters reuse their barriers and buffers
         again = cabi.quant_matmul(x1.cuda(), cuda_view(w), torch.ones(1, device="cuda"), output_dtype=torch.int32).cpu()
         assert torch.equal(again, want)
+    # The cluster kernel on every shape of the list (larger token tiles, several rounds per cluster), forced by
+    # the library's tuning switches; the default rule only picks it where it was measured faster.
+    os.environ["B200Q_W8A8_DECODE"], os.environ["B200Q_W8A8_GEMV"], os.environ["B200Q_W8A8_SMALL_M"] = "1", "0", "0"
+    try:
+        forced = cabi.quant_matmul(x1.cuda(), cuda_view(w), torch.ones(1, device="cuda"), output_dtype=torch.int32).cpu()
+        assert torch.equal(forced, want)
+        check_qmm(cabi, x1, w.t(), scale, pertoken_scale=pt, bias=bias, output_dtype=torch.float16)
+    finally:
+        del os.environ["B200Q_W8A8_DECODE"], os.environ["B200Q_W8A8_GEMV"], os.environ["B200Q_W8A8_SMALL_M"]
+    # ... and the K-split over independent CTAs (int32 scratch, atomics, second kernel), the path of 17..128 tokens
+    os.environ["B200Q_W8A8_DECODE"], os.environ["B200Q_W8A8_GEMV"], os.environ["B200Q_W8A8_SMALL_M"] = "0", "0", "0"
+    try:
+        legacy = cabi.quant_matmul(x1.cuda(), cuda_view(w), torch.ones(1, device="cuda"), output_dtype=torch.int32).cpu()
+        assert torch.equal(legacy, want)
+    finally:
+        del os.environ["B200Q_W8A8_DECODE"], os.environ["B200Q_W8A8_GEMV"], os.environ["B200Q_W8A8_SMALL_M"]
 
 
 def freivalds_and_rows(cabi, q, qo, so, s, weight_nk, scale, seed, rows_checked=64):

@@ -100,6 +100,18 @@ def test_dynamic_quant_asymmetric_matches_oracle(pb, dtype, shape, smooth):
     assert torch.equal(y.cpu(), yo)
 
 
+def test_dynamic_quant_asymmetric_rows_far_from_zero(pb):
+    """Rows whose values sit far from zero compared with their spread: the offset is huge, the sum with it rounds
+    coarsely and the clamp to [-128, 127] matters.  Must still equal the oracle bit for bit."""
+    g = torch.Generator().manual_seed(31)
+    x = (1000.0 + torch.randn((6, 1024), generator=g) * 0.02).to(torch.float16)
+    x[3] = (torch.randn(1024, generator=g) * 3).to(torch.float16)           # an ordinary row among them
+    y, s, o = pb.npu_dynamic_quant_asymmetric(x.cuda())
+    yo, so, oo = oracle.dynamic_quant_asymmetric(x)
+    assert torch.equal(s.cpu().view(torch.int32), so.view(torch.int32)) and torch.equal(o.cpu().view(torch.int32), oo.view(torch.int32))
+    assert torch.equal(y.cpu(), yo)
+
+
 def test_dynamic_quant_asymmetric_constant_and_empty_rows(pb):
     x = torch.full((3, 64), -2.5, dtype=torch.bfloat16)
     x[1] = torch.linspace(-1, 1, 64).to(torch.bfloat16)

@@ -36,9 +36,9 @@ def case(m, k, n, seed, layout):
 def test_static_scratch_matches_workspace_entry_point_twice_in_a_row(cabi):
     lib = cabi.lib()
     assert lib.b200q_static_scratch_bytes() == 16 << 20
-    # m <= 128 splits K across CTAs (int32 accumulators in scratch); the contiguous [k,n] weight
-    # additionally needs the re-layout scratch.  Both calls use the same built-in array.
-    shapes = [(16, 4096, 1024, "nk"), (64, 1024, 2048, "kn"), (128, 4096, 512, "nk"), (3, 512, 384, "kn")]
+    # 17..128 tokens against few channel tiles split K across CTAs (int32 accumulators in scratch); a contiguous
+    # [k,n] weight needs the re-layout scratch, whatever the token count.  All calls use the same built-in array.
+    shapes = [(24, 4096, 1024, "nk"), (64, 1024, 2048, "kn"), (128, 4096, 512, "nk"), (3, 512, 384, "kn")]
     for rep in range(2):
         for i, (m, k, n, layout) in enumerate(shapes):
             x1, x2, scale, pt, bias = case(m, k, n, 100 * rep + i, layout)
