@@ -531,6 +531,8 @@ def run_b200(args):
     dq_ms = time_events(dq_events) / len(dq_events)
     dev_err = _cabi.device_error()
     parity_ok = check_parity(rank, world, device, d, outs, _cabi, dist) if not args.no_parity else None
+    if parity_ok is not None and dev_err != 0:
+        parity_ok = False                                  # a kernel gave up a bounded wait: its output cannot be trusted
     if peers is not None:
         peers.check()
 
