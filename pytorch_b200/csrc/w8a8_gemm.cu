@@ -227,9 +227,12 @@ __device__ __forceinline__ void store_token_rows(const Epi& e, uint32_t taddr, i
 // rows starting at row0 (lane = row).  Results pass through a 4 KB shared-memory staging area private to
 // the warp, 128 bytes of every row at a time (64 16-bit or 32 32-bit outputs), so that eight lanes then
 // write one full 128-byte line of a row and a warp instruction covers four rows: full lines keep the
-// NVLink packets of the remote stores dense.  16-byte chunks are XOR-swizzled by the row so that both
+// NVLink packets of the remote stores dense (256-byte runs with a correspondingly larger staging area and one
+// pipeline stage less were measured slower: 0.45 against 0.42 ms for a link-bound 235 MB push to one peer).  16-byte chunks are XOR-swizzled by the row so that both
 // the row-wise writes and the line-wise reads are free of bank conflicts.  Requires out_dtype in
 // {bf16, f16, f32, i32}, n a multiple of the 128-byte slab and 16-byte aligned destinations.
+constexpr int kPushStageBytes = 32 * 128;                  // per epilogue warp
+
 template <int BN>
 __device__ __forceinline__ void store_token_rows_push(const Epi& e, uint32_t taddr, int64_t row0, int lane,
                                                       int64_t n_tile0, const float* col_f0, const float* col_f1,
@@ -311,7 +314,7 @@ __device__ __forceinline__ void stage_channel_params(const Epi& e, int64_t n_til
   }
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool PUSH = false>
 struct SmemLayout {
   static constexpr int kBTileBytes = BN * kBK;
   static constexpr int kStageBytes = kATileBytes + kBTileBytes;
@@ -319,16 +322,19 @@ struct SmemLayout {
   static constexpr int kBarOff = kTiles;                       // full[S], empty[S], tfull[2], tempty[2]
   static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;   // tmem base, abort flag
   static constexpr int kColOff = kMiscOff + 16;                // 4 x BN 32-bit column parameters
-  static constexpr int kPushOff = (kColOff + 4 * BN * 4 + 127) & ~127;   // 4 KB per epilogue warp (multi-GPU epilogue)
-  static constexpr int kTotal = kPushOff + (kEpiThreads / 32) * 4096;
+  static constexpr int kPushOff = (kColOff + 4 * BN * 4 + 127) & ~127;   // staging per epilogue warp (multi-GPU epilogue)
+  static constexpr int kTotal = kPushOff + (PUSH ? (kEpiThreads / 32) * kPushStageBytes : 0);
   static constexpr int kDynamic = kTotal + 1024;               // slack to align the tiles to 1024 B
 };
 
-template <int BN, int STAGES, bool SWAP>
+// PUSH: the token-row epilogue of the multi-GPU forms (a separate instantiation, so that the single-GPU kernel
+// carries neither its staging areas nor its registers).
+template <int BN, int STAGES, bool SWAP, bool PUSH = false>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Epi e,
                  const Sched s) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, PUSH>;
+  static_assert(!(SWAP && PUSH), "the swapped epilogue does not store to peers");
   constexpr int CH = BN < 32 ? 16 : 32;                 // accumulator columns per tcgen05.ld
   constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
   static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns: power of two <= 512");
@@ -482,14 +488,9 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       } else {
         // D rows are tokens (m), D columns are channels (n).
-        if constexpr (BN >= 64) {
-          if (e.n_dest > 0) {
-            store_token_rows_push<BN>(e, taddr, (int64_t)ta * kTileA + quad * 32, lane, (int64_t)tb * BN, col_f0, col_f1,
-                                      col_f2, col_i, smem_u32(smem + L::kPushOff) + (warp - 2) * 4096);
-          } else {
-            store_token_rows<BN, CH>(e, taddr, (int64_t)ta * kTileA + row_in_tile, (int64_t)tb * BN, col_f0, col_f1,
-                                     col_f2, col_i);
-          }
+        if constexpr (PUSH) {
+          store_token_rows_push<BN>(e, taddr, (int64_t)ta * kTileA + quad * 32, lane, (int64_t)tb * BN, col_f0, col_f1,
+                                    col_f2, col_i, smem_u32(smem + L::kPushOff) + (warp - 2) * kPushStageBytes);
         } else {
           store_token_rows<BN, CH>(e, taddr, (int64_t)ta * kTileA + row_in_tile, (int64_t)tb * BN, col_f0, col_f1, col_f2,
                                    col_i);
@@ -520,7 +521,7 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // halves and write 128 accumulator rows into each CTA's TMEM.  Both CTAs' TMA loads count on the
 // leader's `full` barrier; the leader's tcgen05.commit arrives on both CTAs' `empty` / `tfull`
 // barriers (one commit per CTA, no multicast); both epilogues arrive on the leader's `tempty`.
-template <int STAGES>
+template <int STAGES, bool PUSH = false>
 struct PairLayout {
   static constexpr int kBN = 256;
   static constexpr int kBHalfBytes = 128 * kBK;
@@ -530,15 +531,15 @@ struct PairLayout {
   static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;
   static constexpr int kColOff = kMiscOff + 16;
   static constexpr int kPushOff = (kColOff + 4 * kBN * 4 + 127) & ~127;
-  static constexpr int kTotal = kPushOff + (kEpiThreads / 32) * 4096;
+  static constexpr int kTotal = kPushOff + (PUSH ? (kEpiThreads / 32) * kPushStageBytes : 0);
   static constexpr int kDynamic = kTotal + 1024;
 };
 
-template <int STAGES>
+template <int STAGES, bool PUSH>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Epi e,
                       const Sched s) {
-  using L = PairLayout<STAGES>;
+  using L = PairLayout<STAGES, PUSH>;
   constexpr int BN = L::kBN, CH = 32;
   constexpr uint32_t kTmemCols = 512;
   static_assert(L::kDynamic > 116 * 1024 && L::kDynamic <= 227 * 1024, "one CTA per SM; shared memory budget");
@@ -650,9 +651,9 @@ w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (!epilogue_all(mbar_wait(&tfull[buf], tphase, abort_flag, kDevTimeoutEpilogue))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
-      if (e.n_dest > 0) {
+      if constexpr (PUSH) {
         store_token_rows_push<BN>(e, taddr, (int64_t)ta * 256 + rank * 128 + quad * 32, lane, (int64_t)tb * BN, col_f0,
-                                  col_f1, col_f2, col_i, smem_u32(smem + L::kPushOff) + (warp - 2) * 4096);
+                                  col_f1, col_f2, col_i, smem_u32(smem + L::kPushOff) + (warp - 2) * kPushStageBytes);
       } else {
         store_token_rows<BN, CH>(e, taddr, (int64_t)ta * 256 + rank * 128 + row_in_tile, (int64_t)tb * BN, col_f0, col_f1,
                                  col_f2, col_i);
@@ -1136,11 +1137,11 @@ __global__ void __launch_bounds__(256) transpose_i8_kernel(const int8_t* __restr
   }
 }
 
-template <int BN, int STAGES, bool SWAP>
+template <int BN, int STAGES, bool SWAP, bool PUSH = false>
 int launch_umma(const CUtensorMap& tmA, const CUtensorMap& tmB, const Epi& e, const Sched& s, cudaStream_t st) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, PUSH>;
   static_assert(L::kDynamic <= 227 * 1024, "shared memory budget");
-  constexpr auto kern = w8a8_umma_kernel<BN, STAGES, SWAP>;
+  constexpr auto kern = w8a8_umma_kernel<BN, STAGES, SWAP, PUSH>;
   if (int rc = ensure_dynamic_smem<kern>(L::kDynamic, "quant_matmul")) return rc;
   const int grid = s.units < sm_count() ? s.units : sm_count();
   kern<<<grid, kThreads, L::kDynamic, st>>>(tmA, tmB, e, s);
@@ -1177,10 +1178,10 @@ int resident_clusters(int csize, int dynamic_smem) {
   return cached[dev][csize];
 }
 
-template <int STAGES>
+template <int STAGES, bool PUSH>
 int launch_umma_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Epi& e, const Sched& s, cudaStream_t st) {
-  using L = PairLayout<STAGES>;
-  constexpr auto kern = w8a8_umma_pair_kernel<STAGES>;
+  using L = PairLayout<STAGES, PUSH>;
+  constexpr auto kern = w8a8_umma_pair_kernel<STAGES, PUSH>;
   if (int rc = ensure_dynamic_smem<kern>(L::kDynamic, "quant_matmul")) return rc;
   // As many pairs as can be resident at once (a GPC with an odd number of free SMs leaves one unpaired).
   int pairs = resident_clusters<kern>(2, L::kDynamic);
@@ -1461,7 +1462,8 @@ extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream
     sp.kb_per_split = sp.kblocks;
     sp.splits = 1;
     sp.units = sp.tiles_a * sp.tiles_b;
-    return launch_umma_pair<6>(tmA, tmB, e, sp, st);
+    if (e.n_dest > 0) return launch_umma_pair<6, true>(tmA, tmB, e, sp, st);
+    return launch_umma_pair<6, false>(tmA, tmB, e, sp, st);
   }
 
   Sched s{};
@@ -1494,7 +1496,10 @@ extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream
       default: rc = launch_umma<128, 6, true>(tmA, tmB, e, s, st); break;
     }
   } else {
-    rc = (p.bn == 128) ? launch_umma<128, 6, false>(tmA, tmB, e, s, st) : launch_umma<256, 4, false>(tmA, tmB, e, s, st);
+    if (e.n_dest > 0)
+      rc = (p.bn == 128) ? launch_umma<128, 6, false, true>(tmA, tmB, e, s, st) : launch_umma<256, 4, false, true>(tmA, tmB, e, s, st);
+    else
+      rc = (p.bn == 128) ? launch_umma<128, 6, false>(tmA, tmB, e, s, st) : launch_umma<256, 4, false>(tmA, tmB, e, s, st);
   }
   if (rc) return rc;
   if (e.acc_ws) {
