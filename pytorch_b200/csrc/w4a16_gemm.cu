@@ -150,7 +150,8 @@ template <typename XT>
 __device__ __forceinline__ uint32_t nibbles_to_x2(uint32_t t) {
   using V = typename X2<XT>::type;
   const uint32_t magic = X2<XT>::kMagic;
-  const uint32_t biased = (t & 0x000F000Fu) ^ magic;
+  uint32_t biased;                                   // (t & 0x000F000F) ^ magic as one three-input logic operation
+  asm("lop3.b32 %0, %1, 0x000F000F, %2, 0x6A;" : "=r"(biased) : "r"(t), "r"(magic));
   V w = __hsub2(*reinterpret_cast<const V*>(&biased), *reinterpret_cast<const V*>(&magic));
   return *reinterpret_cast<uint32_t*>(&w);
 }
@@ -666,6 +667,20 @@ __global__ void wq_simt_kernel(const XT* __restrict__ x, const void* __restrict_
   static_cast<XT*>(p.out)[mm * p.n + n] = X2<XT>::from_float(acc);
 }
 
+}  // namespace
+}  // namespace b200q
+#include "w4a16_stream.cuh"
+namespace b200q {
+namespace {
+
+// Few tokens, int4: the streaming warp-MMA kernel (one launch, no workspace) instead of the tcgen05 one.
+bool wq_use_stream(int64_t m, int64_t k, int64_t n, int bits) {
+  if (const char* env = getenv("B200Q_WQ_STREAM")) {                  // tuning override
+    if (env[0] == '0') return false;
+  }
+  return bits == 4 && m <= kWsMaxTokens && n % 32 == 0 && k >= kWsKBlock && k % kWsKBlock == 0;
+}
+
 struct WqPlan {
   int mm;            // tokens per unit: 64 (M = 64 MMAs), 128, or 256 (two M = 128 chunks sharing each weight tile)
   int tiles_n, m_chunks, kblocks, units, ctas, stream_k, max_parts;
@@ -744,8 +759,9 @@ int dispatch_layout(int layout, int mm, const CUtensorMap& tmW, const CUtensorMa
 }  // namespace
 }  // namespace b200q
 
-extern "C" size_t b200q_weight_quant_matmul_workspace_bytes(int64_t m, int64_t k, int64_t n, int /*weight_bits*/) {
+extern "C" size_t b200q_weight_quant_matmul_workspace_bytes(int64_t m, int64_t k, int64_t n, int weight_bits) {
   if (m <= 0 || k <= 0 || n <= 0) return 0;
+  if (b200q::wq_use_stream(m, k, n, weight_bits)) return 0;
   return b200q::wq_plan(m, k, n).ws_bytes;
 }
 
@@ -796,6 +812,12 @@ extern "C" int b200q_weight_quant_matmul(const b200q_weight_quant_matmul_args* a
       wq_simt_kernel<__half><<<grid, block, 0, st>>>(static_cast<const __half*>(a->x), a->weight, a->weight_bits,
                                                      a->w_stride_k, a->w_stride_n, p);
     return check_launch("weight_quant_matmul (simt)");
+  }
+
+  if (layout == kW4N && wq_use_stream(a->m, a->k, a->n, 4) && (a->bias == nullptr || aligned(a->bias, 16)) &&
+      (a->group_size == 0 || a->group_size % kWsKBlock == 0)) {
+    if (a->x_dtype == B200Q_BF16) return dispatch_wq_stream<__nv_bfloat16>(a->x, a->weight, p, st);
+    return dispatch_wq_stream<__half>(a->x, a->weight, p, st);
   }
 
   const WqPlan pl = wq_plan(a->m, a->k, a->n);

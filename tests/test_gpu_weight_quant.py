@@ -61,6 +61,29 @@ def test_w4a16_int4_packed(cabi, m, k, n, gs, dtype):
     check(cabi, d["x"], packed.cpu(), d["antiquant_scale"], None, gs, w_dev=packed)
 
 
+@pytest.mark.parametrize("m,k,n,gs", [(1, 512, 256, 0), (3, 1024, 288, 128), (8, 2048, 1024, 64), (9, 2048, 544, 128),
+                                      (16, 4096, 2080, 256), (12, 8192, 1056, 128), (7, 96, 32, 0)])
+@pytest.mark.parametrize("ksplit", ["", "1", "3", "8"])
+def test_w4a16_few_tokens_streaming_kernel(cabi, monkeypatch, m, k, n, gs, ksplit):
+    """Up to 16 tokens take the streaming warp-MMA kernel: ragged column strips (n not a multiple of 128),
+    warps that start inside a scale group, every split of K over a cluster, bias, both dtypes' roundings."""
+    if ksplit:
+        monkeypatch.setenv("B200Q_WQ_KSPLIT", ksplit)
+    d = workloads.w4a16(m, k, n, gs, 900 + m + n)
+    packed = cabi.int4pack(d["w_int4"].cuda())
+    g = torch.Generator().manual_seed(m)
+    bias = workloads.rand_uniform((n,), g, -1, 1, torch.bfloat16)
+    check(cabi, d["x"], packed.cpu(), d["antiquant_scale"], d["antiquant_offset"], gs, bias=bias, w_dev=packed)
+    check(cabi, d["x"], packed.cpu(), d["antiquant_scale"], None, gs, w_dev=packed)
+    # the tcgen05 kernel dequantises to the same 16-bit values: the two agree far inside the bound
+    got = cabi.weight_quant_matmul(d["x"].cuda(), packed, d["antiquant_scale"].cuda(), d["antiquant_offset"].cuda(),
+                                   antiquant_group_size=gs)
+    monkeypatch.setenv("B200Q_WQ_STREAM", "0")
+    other = cabi.weight_quant_matmul(d["x"].cuda(), packed, d["antiquant_scale"].cuda(), d["antiquant_offset"].cuda(),
+                                     antiquant_group_size=gs)
+    assert oracle.max_mixed_error(got.cpu(), other.cpu()) <= 2.0 ** -8
+
+
 @pytest.mark.parametrize("m,k,n,gs", [(1, 512, 128, 0), (33, 1024, 272, 0), (128, 512, 256, 128), (260, 1024, 128, 64)])
 @pytest.mark.parametrize("layout", ["nk_view", "kn"])
 def test_w8a16_int8(cabi, m, k, n, gs, layout):
