@@ -21,6 +21,7 @@
 #include <stdlib.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -300,6 +301,62 @@ __device__ __forceinline__ void store_token_rows_push(const Epi& e, uint32_t tad
   }
 }
 
+// Replicating epilogue through TMA stores (16-bit outputs, CTA-pair kernel): the four epilogue warps write a
+// 128-row x 64-column chunk of the tile into a 128B-swizzled staging buffer, one thread issues a bulk tensor
+// store of the chunk into the local matrix and into every peer's, and the warps go on to the next chunk in
+// another buffer.  The accumulator buffer in tensor memory is released as soon as its last chunk is in shared
+// memory, so the MMAs of the next tile overlap the stores over NVLink.  Rows beyond m and columns beyond n are
+// clipped by the tensor maps.
+constexpr int kTmaStoreBufs = 3;
+constexpr int kTmaStoreBufBytes = 128 * 128;               // 128 rows x 64 two-byte columns
+struct OutMaps {
+  CUtensorMap m[kMaxDest + 1];                             // [0] the local matrix, [1..n_dest] the peers'
+};
+struct NoOutMaps {};
+
+template <int BN>
+__device__ __forceinline__ void store_token_rows_tma(const Epi& e, const OutMaps& om, uint32_t taddr, int64_t cta_row0,
+                                                     int quad, int lane, bool issuer, int64_t n_tile0,
+                                                     const float* col_f0, const float* col_f1, const float* col_f2,
+                                                     const int* col_i, uint32_t stage_base, uint32_t& chunk) {
+  const int64_t mm = cta_row0 + quad * 32 + lane;
+  const float pt = (mm < e.m && (e.flags & kHasPt)) ? __ldg(e.pertoken + mm) : 1.0f;
+  const uint32_t row = (uint32_t)(quad * 32 + lane);
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 64) {
+    if (n_tile0 + c0 >= e.n) break;                        // same decision in every thread
+    uint32_t w[32];                                        // this row's 128 bytes
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t r[32];
+      __syncwarp();
+      tmem_ld_x32(taddr + c0 + 32 * h, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const int cj = c0 + 32 * h + j;
+        const float v0 = dequant((int)r[j], col_i[cj], col_f0[cj], pt, col_f2[cj], col_f1[cj], e.flags);
+        const float v1 = dequant((int)r[j + 1], col_i[cj + 1], col_f0[cj + 1], pt, col_f2[cj + 1], col_f1[cj + 1], e.flags);
+        w[16 * h + j / 2] = to_bits16(v0, e.out_dtype) | (to_bits16(v1, e.out_dtype) << 16);
+      }
+    }
+    const uint32_t buf = stage_base + (chunk % kTmaStoreBufs) * kTmaStoreBufBytes;
+    named_barrier_sync(2, kEpiThreads);                    // the issuer has seen this buffer's last stores read it
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      st_shared_v4(buf + row * 128 + ((c ^ (row & 7)) << 4), make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
+    fence_proxy_async_smem();
+    named_barrier_sync(3, kEpiThreads);
+    if (issuer) {
+      if (cta_row0 < e.m)                                  // a box that starts beyond the last row is not issued at all
+        for (int d = 0; d <= e.n_dest; ++d) tma_store_2d(&om.m[d], buf, (int)(n_tile0 + c0), (int)cta_row0);
+      bulk_commit_group();
+      bulk_wait_group_read<kTmaStoreBufs - 1>();           // the buffer of the next chunk is free again
+    }
+    ++chunk;
+  }
+}
+
 // Per-channel parameters of the BN columns starting at n_tile0 -> shared memory, by the epilogue threads.
 template <int BN>
 __device__ __forceinline__ void stage_channel_params(const Epi& e, int64_t n_tile0, int et, float* col_f0, float* col_f1,
@@ -521,7 +578,9 @@ w8a8_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // halves and write 128 accumulator rows into each CTA's TMEM.  Both CTAs' TMA loads count on the
 // leader's `full` barrier; the leader's tcgen05.commit arrives on both CTAs' `empty` / `tfull`
 // barriers (one commit per CTA, no multicast); both epilogues arrive on the leader's `tempty`.
-template <int STAGES, bool PUSH = false>
+// EPI: 0 plain stores to `out`; 1 plain stores to `out` and the peers (any output type, routed form);
+// 2 TMA stores to `out` and the peers (16-bit outputs, replicate form).
+template <int STAGES, int EPI = 0>
 struct PairLayout {
   static constexpr int kBN = 256;
   static constexpr int kBHalfBytes = 128 * kBK;
@@ -530,16 +589,17 @@ struct PairLayout {
   static constexpr int kBarOff = kTiles;
   static constexpr int kMiscOff = kBarOff + (2 * STAGES + 4) * 8;
   static constexpr int kColOff = kMiscOff + 16;
-  static constexpr int kPushOff = (kColOff + 4 * kBN * 4 + 127) & ~127;
-  static constexpr int kTotal = kPushOff + (PUSH ? (kEpiThreads / 32) * kPushStageBytes : 0);
+  static constexpr int kPushOff = (kColOff + 4 * kBN * 4 + 1023) & ~1023;
+  static constexpr int kTotal = kPushOff + (EPI == 1 ? (kEpiThreads / 32) * kPushStageBytes
+                                            : EPI == 2 ? kTmaStoreBufs * kTmaStoreBufBytes : 0);
   static constexpr int kDynamic = kTotal + 1024;
 };
 
-template <int STAGES, bool PUSH>
+template <int STAGES, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Epi e,
-                      const Sched s) {
-  using L = PairLayout<STAGES, PUSH>;
+                      const Sched s, const __grid_constant__ std::conditional_t<EPI == 2, OutMaps, NoOutMaps> om) {
+  using L = PairLayout<STAGES, EPI>;
   constexpr int BN = L::kBN, CH = 32;
   constexpr uint32_t kTmemCols = 512;
   static_assert(L::kDynamic > 116 * 1024 && L::kDynamic <= 227 * 1024, "one CTA per SM; shared memory budget");
@@ -643,6 +703,11 @@ w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int row_in_tile = quad * 32 + lane;
     int buf = 0;
     uint32_t tphase = 0;
+    uint32_t chunk = 0;
+    if constexpr (EPI == 2) {
+      if (et == 0)
+        for (int d = 0; d <= e.n_dest; ++d) prefetch_tensormap(&om.m[d]);
+    }
     for (int u = pair; u < s.units; u += npairs) {
       const int ta = u % s.tiles_a, tb = u / s.tiles_a;
       named_barrier_sync(1, kEpiThreads);
@@ -651,7 +716,10 @@ w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (!epilogue_all(mbar_wait(&tfull[buf], tphase, abort_flag, kDevTimeoutEpilogue))) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
-      if constexpr (PUSH) {
+      if constexpr (EPI == 2) {
+        store_token_rows_tma<BN>(e, om, taddr, (int64_t)ta * 256 + rank * 128, quad, lane, et == 0, (int64_t)tb * BN, col_f0,
+                                 col_f1, col_f2, col_i, smem_u32(smem + L::kPushOff), chunk);
+      } else if constexpr (EPI == 1) {
         store_token_rows_push<BN>(e, taddr, (int64_t)ta * 256 + rank * 128 + quad * 32, lane, (int64_t)tb * BN, col_f0,
                                   col_f1, col_f2, col_i, smem_u32(smem + L::kPushOff) + (warp - 2) * kPushStageBytes);
       } else {
@@ -662,6 +730,9 @@ w8a8_umma_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[buf]), 0));
       if (++buf == 2) { buf = 0; tphase ^= 1; }
+    }
+    if constexpr (EPI == 2) {
+      if (et == 0) bulk_wait_group<0>();                   // every store of this CTA has been performed
     }
   }
 
@@ -1178,15 +1249,18 @@ int resident_clusters(int csize, int dynamic_smem) {
   return cached[dev][csize];
 }
 
-template <int STAGES, bool PUSH>
-int launch_umma_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Epi& e, const Sched& s, cudaStream_t st) {
-  using L = PairLayout<STAGES, PUSH>;
-  constexpr auto kern = w8a8_umma_pair_kernel<STAGES, PUSH>;
+template <int STAGES, int EPI>
+int launch_umma_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Epi& e, const Sched& s, cudaStream_t st,
+                     const OutMaps* om = nullptr) {
+  using L = PairLayout<STAGES, EPI>;
+  constexpr auto kern = w8a8_umma_pair_kernel<STAGES, EPI>;
   if (int rc = ensure_dynamic_smem<kern>(L::kDynamic, "quant_matmul")) return rc;
-  // As many pairs as can be resident at once (a GPC with an odd number of free SMs leaves one unpaired).
+  // Pairs that can be resident at once (cluster scheduling may leave an SM of a GPC unused).
   int pairs = resident_clusters<kern>(2, L::kDynamic);
   if (s.units < pairs) pairs = s.units;
-  kern<<<2 * pairs, kThreads, L::kDynamic, st>>>(tmA, tmB, e, s);   // cluster dims (2,1,1) are a kernel attribute
+  // cluster dims (2,1,1) are a kernel attribute
+  if constexpr (EPI == 2) kern<<<2 * pairs, kThreads, L::kDynamic, st>>>(tmA, tmB, e, s, *om);
+  else kern<<<2 * pairs, kThreads, L::kDynamic, st>>>(tmA, tmB, e, s, NoOutMaps{});
   return check_launch("quant_matmul (tcgen05, CTA pairs)");
 }
 
@@ -1462,8 +1536,24 @@ extern "C" int b200q_quant_matmul(const b200q_quant_matmul_args* a, void* stream
     sp.kb_per_split = sp.kblocks;
     sp.splits = 1;
     sp.units = sp.tiles_a * sp.tiles_b;
-    if (e.n_dest > 0) return launch_umma_pair<6, true>(tmA, tmB, e, sp, st);
-    return launch_umma_pair<6, false>(tmA, tmB, e, sp, st);
+    if (e.n_dest > 0) {
+      const bool two_byte = e.out_dtype == B200Q_BF16 || e.out_dtype == B200Q_F16;
+      bool tma_stores = two_byte && e.route_rows == 0 && e.ldo % 8 == 0;
+      if (const char* env = getenv("B200Q_W8A8_TMA_STORE")) tma_stores = tma_stores && env[0] != '0';   // tuning override
+      if (tma_stores) {
+        OutMaps om;
+        for (int d = 0; d <= e.n_dest; ++d) {
+          void* base = d == 0 ? e.out : e.dest[d - 1];
+          if (int rc = make_tmap_2d_cached(&om.m[d], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, base, (uint64_t)e.n, (uint64_t)e.m,
+                                           (uint64_t)e.ldo * 2, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B,
+                                           "quant_matmul (output, TMA store)"))
+            return rc;
+        }
+        return launch_umma_pair<5, 2>(tmA, tmB, e, sp, st, &om);
+      }
+      return launch_umma_pair<6, 1>(tmA, tmB, e, sp, st);
+    }
+    return launch_umma_pair<6, 0>(tmA, tmB, e, sp, st);
   }
 
   Sched s{};
