@@ -13,12 +13,23 @@
 namespace b200q {
 namespace {
 
-// (silu(a.x) * b.x, silu(a.y) * b.y) with silu(a) = a * (1 / (1 + exp(-a))); exp(-a) = inf for very negative a
-// gives a * 0.  The reciprocal is the correctly rounded one (the same value an IEEE division of 1 by the sum
-// gives, at a fraction of its instructions); sums and products run as packed two-wide fp32 instructions.
+__device__ __forceinline__ float rcp_approx(float d) {
+  float y;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(d));
+  return y;
+}
+
+// (silu(a.x) * b.x, silu(a.y) * b.y) with silu(a) = a * (1 / (1 + exp(-a))).  The exponent is capped at 80, so
+// the sum stays a normal number (for a < -80 the result is below 2e-33 in magnitude either way).  The
+// reciprocal of a normal number: the hardware approximation (within one ulp) and one Newton step in two
+// fused multiply-adds, which rounds like an IEEE division of 1 by the sum without that routine's checks for
+// special operands.  Sums, products and the Newton step run as packed two-wide fp32 instructions.
 __device__ __forceinline__ float2 silu_mul2(float2 a, float2 b) {
-  const float2 d = __fadd2_rn(make_float2(1.0f, 1.0f), make_float2(__expf(-a.x), __expf(-a.y)));
-  const float2 s = make_float2(__frcp_rn(d.x), __frcp_rn(d.y));
+  const float2 one = make_float2(1.0f, 1.0f);
+  const float2 d = __fadd2_rn(one, make_float2(__expf(fminf(-a.x, 80.0f)), __expf(fminf(-a.y, 80.0f))));
+  const float2 y0 = make_float2(rcp_approx(d.x), rcp_approx(d.y));
+  const float2 err = __ffma2_rn(make_float2(-d.x, -d.y), y0, one);
+  const float2 s = __ffma2_rn(y0, err, y0);
   return __fmul2_rn(__fmul2_rn(a, s), b);
 }
 

@@ -75,13 +75,14 @@ def test_w4a16_few_tokens_streaming_kernel(cabi, monkeypatch, m, k, n, gs, kspli
     bias = workloads.rand_uniform((n,), g, -1, 1, torch.bfloat16)
     check(cabi, d["x"], packed.cpu(), d["antiquant_scale"], d["antiquant_offset"], gs, bias=bias, w_dev=packed)
     check(cabi, d["x"], packed.cpu(), d["antiquant_scale"], None, gs, w_dev=packed)
-    # the tcgen05 kernel dequantises to the same 16-bit values: the two agree far inside the bound
+    # the tcgen05 kernel dequantises to the same 16-bit values; the fp32 sums are taken in another order, which
+    # can move an output by one unit in the last place of its 16-bit format (at most 2**-7 relative)
     got = cabi.weight_quant_matmul(d["x"].cuda(), packed, d["antiquant_scale"].cuda(), d["antiquant_offset"].cuda(),
                                    antiquant_group_size=gs)
     monkeypatch.setenv("B200Q_WQ_STREAM", "0")
     other = cabi.weight_quant_matmul(d["x"].cuda(), packed, d["antiquant_scale"].cuda(), d["antiquant_offset"].cuda(),
                                      antiquant_group_size=gs)
-    assert oracle.max_mixed_error(got.cpu(), other.cpu()) <= 2.0 ** -8
+    assert oracle.max_mixed_error(got.cpu(), other.cpu()) <= TOL
 
 
 @pytest.mark.parametrize("m,k,n,gs", [(1, 512, 128, 0), (33, 1024, 272, 0), (128, 512, 256, 128), (260, 1024, 128, 64)])
