@@ -417,12 +417,12 @@ def run_b200(args):
         # an NCCL all-gather + re-interleave copy is used only where that memory cannot be set up
         # (BENCH_EXCHANGE=nccl forces it).
         try:
-            if os.environ.get("BENCH_EXCHANGE", "p2p") != "p2p":
+            if os.environ.get("BENCH_EXCHANGE", "p2p") not in ("p2p", "fused"):
                 raise RuntimeError("NCCL exchange requested")
             peers = sharded.PeerGroup(device)
             gat_gu = sharded.PeerColumnGather(M, 2 * FFN, torch.bfloat16, device, peers)
             gat_dn = sharded.PeerColumnGather(M, HIDDEN, torch.bfloat16, device, peers)
-            exchange = "gemm_epilogue_peer_stores"
+            exchange = "copy_engine_pipelined" if os.environ.get("BENCH_EXCHANGE", "p2p") == "p2p" else "gemm_epilogue_peer_stores"
         except Exception as exc:                                   # noqa: BLE001
             if rank == 0:
                 print(f"[bench] peer-memory exchange unavailable ({exc}); using NCCL all-gather", file=sys.stderr)
@@ -444,6 +444,31 @@ def run_b200(args):
             nopush = (sharded.ShardedW8A8LinearPlan(x, smooth, w_gu, s_gu, gat_gu, fused_push=False),
                       sharded.ShardedW8A8LinearPlan(x_down, smooth_down, w_dn, s_dn, gat_dn, fused_push=False))
     gemm_events, dq_events = [], []
+    pipe = sharded.PipelinedExchange(peers, (gat_gu, gat_dn), device) if exchange == "copy_engine_pipelined" else None
+
+    def step_pipelined(xi, xdi, record=False):
+        """The same four kernels writing only their own column blocks; each block goes to the peers on the copy
+        engines behind its GEMM, on a side stream, followed there by the cross-rank barrier, while this
+        stream goes on with the next step (two result buffers; step i+2 waits for step i's copies)."""
+        e = [ev() for _ in range(5)] if record else None
+        pipe.begin_step()
+        if record: e[0].record()
+        nopush[0].quant(xi)
+        if record: e[1].record()
+        nopush[1].quant(xdi)
+        if record: e[2].record()
+        nopush[0].matmul(push=False)
+        if record: e[3].record()
+        pipe.produced(0)
+        nopush[1].matmul(push=False)
+        if record: e[4].record()
+        pipe.produced(1)
+        o1, o2 = gat_gu.full, gat_dn.full
+        pipe.end_step()
+        if record:
+            dq_events.extend([(e[0], e[1]), (e[1], e[2])])
+            gemm_events.extend([(e[2], e[3]), (e[3], e[4])])
+        return o1, o2
 
     def step(xi, xdi, record=False):
         """One pass of the path: both dynamic quantisations, then both GEMMs (the two projections of this
@@ -499,13 +524,17 @@ def run_b200(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    headline_step = step_pipelined if pipe is not None else step
+
     def timed_steps(n, record=False):
         barrier()
         t0, t1 = ev(), ev()
         t0.record()
         h0 = time.perf_counter()
         for _ in range(n):
-            step(x, x_down, record)
+            headline_step(x, x_down, record)
+        if pipe is not None:
+            pipe.drain()                                   # the last steps' copies and barriers are inside the interval
         t1.record()
         host_ms = (time.perf_counter() - h0) * 1e3 / n
         barrier()
@@ -513,7 +542,7 @@ def run_b200(args):
 
     # ---- device-resident measurement
     for _ in range(args.warmup):
-        step(x, x_down)
+        headline_step(x, x_down)
     barrier()
     # Only the rank that prints the line samples its GPU: eight processes polling NVML at this rate
     # would contend with each other's kernel launches.  The sampler is set up before the last barrier,
@@ -527,7 +556,7 @@ def run_b200(args):
     value = step_flops() / (ms_step * 1e-3) / 1e12
     # per-kernel events from extra steps through the same path (same kernels, same buffers)
     timed_steps(4, record=True)
-    outs = step(x, x_down)
+    outs = headline_step(x, x_down)
     barrier()
     gemm_ms = time_events(gemm_events) / len(gemm_events)
     dq_ms = time_events(dq_events) / len(dq_events)
@@ -664,6 +693,21 @@ def measure_multi_gpu_extras(c, args):
     out["exposed_exchange_ms_per_step"] = round(c["ms_step"] - cms, 4)
     recv = (world - 1) / world * (M * 2 * FFN + M * HIDDEN) * 2
     out["gather_link_floor_ms"] = round(recv / 770e9 * 1e3, 4)
+    if c["exchange"] == "copy_engine_pipelined":
+        # -- the same step with the exchange fused into the GEMM's epilogue (one kernel computes and stores to the peers)
+        for _ in range(3):
+            c["step"](c["x"], c["x_down"])
+        barrier()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(args.steps):
+            c["step"](c["x"], c["x_down"])
+        b.record()
+        barrier()
+        fms = mor(a.elapsed_time(b)) / args.steps
+        out["fused_epilogue_form"] = {"ms_per_step": round(fms, 4), "value": round(step_flops() / (fms * 1e-3) / 1e12, 2),
+                                      "unit": UNIT, "note": "exchange = gemm_epilogue_peer_stores: each GEMM launch also stores "
+                                      "its tiles into every peer's matrix (TMA tensor stores), one barrier per step"}
 
     # -- tensor-parallel form
     lib = _cabi.lib()
@@ -878,10 +922,13 @@ def run_and_print(args):
     if world > 1:
         out.update(multi)
         out["exchange"] = c["exchange"]
-        out["exchange_note"] = ("gemm_epilogue_peer_stores: the GEMM's epilogue stores each finished tile into the local "
-                                "[M,N] matrix and into every peer's (128-bit stores over NVLink, full 128-byte lines), one "
-                                "bounded barrier per step; nccl_all_gather: all_gather_into_tensor plus one re-interleave "
-                                "copy.  link floor = bytes each GPU must receive / 770 GB/s")
+        out["exchange_note"] = ("copy_engine_pipelined: every GEMM writes its own column block; behind it, on a side stream, "
+                                "one strided copy-engine transfer per peer and the bounded cross-rank barrier, while the "
+                                "kernels of the next step run (two result buffers; all copies and barriers of the timed "
+                                "steps end inside the timed interval); gemm_epilogue_peer_stores: the GEMM's epilogue "
+                                "stores each finished tile into the local [M,N] matrix and into every peer's (TMA tensor "
+                                "stores), one bounded barrier per step; nccl_all_gather: all_gather_into_tensor plus one "
+                                "re-interleave copy.  link floor = bytes each GPU must receive / 770 GB/s")
     if rank == 0 and world == 1 and not args.no_extras:
         out["other_configs"] = other_configs(_cabi, peaks)
         out["cpu_baseline"] = cpu_baseline()

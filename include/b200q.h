@@ -216,6 +216,16 @@ int b200q_anti_quant(const void* x, int src_bits, const void* scale, const void*
 int b200q_scatter_columns(const void* src, void* const* peer_dst, int n_peers, int64_t rows,
                           int64_t row_stride_bytes, int64_t col_offset_bytes, int64_t block_bytes, void* stream);
 
+/* The same exchange on the copy engines: one strided device-to-device copy per peer (cudaMemcpy2DAsync) of
+ * bytes [col_offset, col_offset + block_bytes) of every row, queued on `stream` in the order of `peer_dst`.
+ * No SM is used, so a side stream can carry the exchange of one step while the kernels of the next one run;
+ * the caller orders it after the producing GEMM with an event and runs the cross-rank barrier behind it on
+ * the same stream.  Same arguments as b200q_scatter_columns; no alignment rule.
+ *   replaces hcclAllGather in ProcessGroupHCCL::_allgather_base
+ *   (torch_npu/csrc/distributed/ProcessGroupHCCL.cpp:5896-5956) for this path. */
+int b200q_copy_columns(const void* src, void* const* peer_dst, int n_peers, int64_t rows, int64_t row_stride_bytes,
+                       int64_t col_offset_bytes, int64_t block_bytes, void* stream);
+
 /* Cross-rank barrier for the multi-GPU epilogues above: `flags` is a HOST array of `world` device
  * pointers, flags[i] = rank i's array of `world` zero-initialised uint32 words, mapped for peer access.
  * Rank `rank` announces `epoch` (1, 2, 3 ... the same on every rank for the same barrier) to every peer

@@ -27,7 +27,7 @@ EXPORTS = (
     "b200q_weight_quant_matmul_workspace_bytes", "b200q_weight_quant_matmul", "b200q_int4pack",
     "b200q_trans_quant_param", "b200q_scatter_columns", "b200q_dynamic_quant_ext", "b200q_anti_quant",
     "b200q_swiglu_quant", "b200q_enable_host_error_word", "b200q_peek_device_error", "b200q_selftest_expire_wait",
-    "b200q_peer_barrier", "b200q_reduce_slots",
+    "b200q_peer_barrier", "b200q_reduce_slots", "b200q_copy_columns",
 )
 
 
@@ -109,6 +109,7 @@ def lib() -> C.CDLL:
                                          C.POINTER(C.c_void_p), C.c_int, C.c_void_p]
         l.b200q_scatter_columns.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int64, C.c_int64, C.c_int64,
                                             C.c_int64, C.c_void_p]
+        l.b200q_copy_columns.argtypes = l.b200q_scatter_columns.argtypes
         _lib = l
     return _lib
 
@@ -323,6 +324,18 @@ def scatter_columns(full: torch.Tensor, peer_ptrs, col_lo: int, col_hi: int) -> 
     arr = (C.c_void_p * max(len(peer_ptrs), 1))(*[C.c_void_p(int(p)) for p in peer_ptrs])
     check(lib().b200q_scatter_columns(_ptr(full), arr, len(peer_ptrs), full.shape[0], full.shape[1] * es,
                                       col_lo * es, (col_hi - col_lo) * es, _stream()))
+
+
+def copy_columns(full: torch.Tensor, peer_ptrs, col_lo: int, col_hi: int) -> None:
+    """``b200q_copy_columns``: the push of :func:`scatter_columns` as one copy-engine transfer per peer,
+    queued on the current stream."""
+    _need_cuda(full)
+    if full.dim() != 2 or not full.is_contiguous():
+        raise B200QError(ERR_BAD_ARG, "copy_columns: a contiguous 2-D matrix is required")
+    es = full.element_size()
+    arr = (C.c_void_p * max(len(peer_ptrs), 1))(*[C.c_void_p(int(p)) for p in peer_ptrs])
+    check(lib().b200q_copy_columns(_ptr(full), arr, len(peer_ptrs), full.shape[0], full.shape[1] * es,
+                                   col_lo * es, (col_hi - col_lo) * es, _stream()))
 
 
 def reduce_slots(slots: torch.Tensor, out: torch.Tensor, peer_out=()) -> torch.Tensor:

@@ -209,3 +209,26 @@ extern "C" int b200q_scatter_columns(const void* src, void* const* peer_dst, int
       static_cast<const uint8_t*>(src), peers, rows, row_stride_bytes, col_offset_bytes, vecs_per_row);
   return check_launch("scatter_columns");
 }
+
+extern "C" int b200q_copy_columns(const void* src, void* const* peer_dst, int n_peers, int64_t rows,
+                                  int64_t row_stride_bytes, int64_t col_offset_bytes, int64_t block_bytes,
+                                  void* stream) {
+  using namespace b200q;
+  clear_error();
+  B200Q_REQUIRE(n_peers >= 0 && n_peers <= kMaxPeers, B200Q_ERR_BAD_ARG, "copy_columns: 0..%d peers, got %d", kMaxPeers,
+                n_peers);
+  B200Q_REQUIRE(rows >= 0 && block_bytes >= 0 && col_offset_bytes >= 0 &&
+                    col_offset_bytes + block_bytes <= row_stride_bytes,
+                B200Q_ERR_BAD_ARG, "copy_columns: column block does not fit the row");
+  if (n_peers == 0 || rows == 0 || block_bytes == 0) return B200Q_OK;
+  B200Q_REQUIRE(src != nullptr && peer_dst != nullptr, B200Q_ERR_BAD_ARG, "copy_columns: NULL pointer");
+  const uint8_t* from = static_cast<const uint8_t*>(src) + col_offset_bytes;
+  for (int i = 0; i < n_peers; ++i) {
+    B200Q_REQUIRE(peer_dst[i] != nullptr, B200Q_ERR_BAD_ARG, "copy_columns: peer %d pointer is NULL", i);
+    cudaError_t err = cudaMemcpy2DAsync(static_cast<uint8_t*>(peer_dst[i]) + col_offset_bytes, (size_t)row_stride_bytes,
+                                        from, (size_t)row_stride_bytes, (size_t)block_bytes, (size_t)rows,
+                                        cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
+    if (err != cudaSuccess) return fail(B200Q_ERR_LAUNCH, "copy_columns: peer %d: %s", i, cudaGetErrorString(err));
+  }
+  return B200Q_OK;
+}

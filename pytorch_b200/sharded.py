@@ -158,6 +158,11 @@ class PeerColumnGather:
         from . import _cabi
         _cabi.scatter_columns(self.full, self.peer_ptrs, self.lo, self.hi)
 
+    def push_copy_engine(self) -> None:
+        """The same push as one copy-engine transfer per peer on the current stream (no SM involved)."""
+        from . import _cabi
+        _cabi.copy_columns(self.full, self.peer_ptrs, self.lo, self.hi)
+
     def finish(self) -> torch.Tensor:
         self.peers.barrier()
         return self.full
@@ -166,6 +171,62 @@ class PeerColumnGather:
         """Push kernel + barrier: the exchange as a separate step after a GEMM that wrote only locally."""
         self.push()
         return self.finish()
+
+
+class PipelinedExchange:
+    """The exchange of a step on the copy engines, one step behind the kernels.
+
+    The GEMMs of a step write only their own column blocks (``fused_push=False`` plans).  After each GEMM the
+    caller calls :meth:`produced`: an event is recorded on the compute stream and, on a side stream, the
+    column block is copied into every peer's matrix behind that event.  :meth:`end_step` queues the
+    cross-rank barrier behind the copies, on the side stream too, and rotates the result buffers.  The
+    compute stream never waits for NVLink: with two result buffers per gather the kernels of step i+1 run
+    while the blocks of step i cross the links, and step i+2 (which writes the buffers of step i again)
+    first waits for step i's copies.  :meth:`drain` makes the compute stream wait for everything queued.
+
+    Whoever reads a gathered matrix of step i must (a) wait for ``done_event(i)`` and (b) have finished, or be
+    queued on the side stream through :meth:`before_next_barrier`, before this rank joins the barrier of step
+    i+1: peers write that matrix again in their step i+2, which they start once that barrier has passed."""
+
+    def __init__(self, peers: PeerGroup, gathers, device):
+        self.peers, self.gathers = peers, list(gathers)
+        self.side = torch.cuda.Stream(device=device)
+        nbuf = len(self.gathers[0].bufs)
+        assert nbuf >= 2 and all(len(g.bufs) == nbuf for g in self.gathers)
+        self._done = [torch.cuda.Event() for _ in range(nbuf)]
+        self._produced = [[torch.cuda.Event() for _ in self.gathers] for _ in range(nbuf)]
+        self._steps = 0
+
+    def begin_step(self) -> None:
+        """Before the first kernel that writes this step's result buffers."""
+        if self._steps >= len(self._done):
+            torch.cuda.current_stream().wait_event(self._done[self.gathers[0].cur])
+
+    def produced(self, index: int) -> None:
+        """The GEMM of gather ``index`` has been queued on the current stream."""
+        g = self.gathers[index]
+        ev = self._produced[g.cur][index]
+        ev.record(torch.cuda.current_stream())
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ev)
+            g.push_copy_engine()
+
+    def before_next_barrier(self, event: torch.cuda.Event) -> None:
+        """A reader of an earlier step's gathered matrix has recorded ``event`` when it was done."""
+        self.side.wait_event(event)
+
+    def end_step(self) -> torch.cuda.Event:
+        b = self.gathers[0].cur
+        with torch.cuda.stream(self.side):
+            self.peers.barrier()
+            self._done[b].record(self.side)
+        for g in self.gathers:
+            g.advance()
+        self._steps += 1
+        return self._done[b]
+
+    def drain(self) -> None:
+        torch.cuda.current_stream().wait_stream(self.side)
 
 
 class LocalOutput:

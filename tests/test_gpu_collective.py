@@ -43,6 +43,22 @@ def test_epilogue_replicates_the_column_block_to_every_peer(cabi, m, k, n, world
     assert cabi.device_error() == 0
 
 
+def test_copy_engine_push_writes_the_column_block_and_nothing_else(cabi):
+    g = torch.Generator().manual_seed(11)
+    full = torch.randn((300, 1000), generator=g).to(torch.bfloat16).cuda()
+    peers = [torch.full((300, 1000), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    lo, hi = 250, 500
+    cabi.copy_columns(full, [p.data_ptr() for p in peers], lo, hi)
+    torch.cuda.synchronize()
+    for p in peers:
+        assert torch.equal(p[:, lo:hi], full[:, lo:hi])
+        assert bool((p[:, :lo] == 7.0).all()) and bool((p[:, hi:] == 7.0).all())
+    by_kernel = [torch.full((300, 1000), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    cabi.scatter_columns(full, [p.data_ptr() for p in by_kernel], 248, 504)   # the kernel push wants 16-byte multiples
+    torch.cuda.synchronize()
+    assert torch.equal(by_kernel[0][:, lo:hi], peers[0][:, lo:hi])
+
+
 def test_replicating_epilogue_rejects_what_it_cannot_write(cabi):
     x1 = torch.zeros(64, 64, dtype=torch.int8, device="cuda")
     w = torch.zeros(96, 64, dtype=torch.int8, device="cuda")

@@ -96,6 +96,23 @@ def _rank_main(rank, world, port, results):
             torch.cuda.synchronize()
             ok = ok and torch.equal(full.cpu().view(torch.int16), want.view(torch.int16))
             gat.advance()
+        # the exchange on the copy engines, one step behind the kernels (two steps in flight, buffers reused)
+        nop = sharded.ShardedW8A8LinearPlan(d["x"].to(dev), d["smooth_scales"].to(dev), w.to(dev), sc.to(dev), gat,
+                                            fused_push=False)
+        pipe = sharded.PipelinedExchange(peers, (gat,), dev)
+        fulls, dones = [], []
+        for _ in range(5):
+            pipe.begin_step()
+            nop.quant()
+            nop.matmul(push=False)
+            pipe.produced(0)
+            fulls.append(gat.full)
+            dones.append(pipe.end_step())
+        pipe.drain()
+        torch.cuda.synchronize()
+        dist.barrier()
+        for full in fulls[-2:]:                           # the two result matrices hold the last two steps
+            ok = ok and torch.equal(full.cpu().view(torch.int16), want.view(torch.int16))
         # collective-fused operators against the oracle of all ranks' inputs (same seed on every rank)
         g = torch.Generator().manual_seed(5)
         mm, kk, nn = 128, 256, 256
