@@ -58,12 +58,15 @@ __device__ __forceinline__ int quant_asym_exact(float f, float scale, float offs
 // offset is moderate, which the caller checks, so no clamp.
 // Packed two-wide fp32 instructions; a constant row (scale 0) gives 0, a scale too small for a finite
 // reciprocal (inv is NaN) takes true divisions.
+// MODE 0: packed path; 1: true divisions with the clamp; 2: constant row (scale 0), all zeros.  The mode is the
+// same for a whole row, so the caller branches once per row, not once per vector.
+template <int MODE>
 __device__ __forceinline__ uint2 quantize8_asym(const float (&f)[8], float scale, float inv, float offset) {
   uint32_t u[8];
-  if (scale == 0.0f) {
+  if (MODE == 2) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) u[j] = 0u;
-  } else if (inv == inv) {
+  } else if (MODE == 0) {
     const float2 inv2 = make_float2(inv, inv), nscale2 = make_float2(-scale, -scale), off2 = make_float2(offset, offset);
     const float2 magic2 = make_float2(12582912.0f, 12582912.0f);
 #pragma unroll
@@ -117,13 +120,14 @@ dynamic_quant_ext_rows(const T* __restrict__ x, const ST* __restrict__ smooth, c
     for (int i = 0; i < ITERS; ++i) {
       const int v = min((int)(threadIdx.x + i * blockDim.x), nvec - 1);
       const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-      float sm[8];
+      float2 sm[4];
       if (smooth != nullptr) load_smooth8(sm_row + v * 8, sm);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float2 pr = unpack2<T>(w[j]);
-        f[i][2 * j] = smooth != nullptr ? __fmul_rn(pr.x, sm[2 * j]) : pr.x;
-        f[i][2 * j + 1] = smooth != nullptr ? __fmul_rn(pr.y, sm[2 * j + 1]) : pr.y;
+        float2 pr = unpack2<T>(w[j]);
+        if (smooth != nullptr) pr = __fmul2_rn(pr, sm[j]);
+        f[i][2 * j] = pr.x;
+        f[i][2 * j + 1] = pr.y;
         mx = fmaxf(mx, fmaxf(f[i][2 * j], f[i][2 * j + 1]));
         mn = fminf(mn, fminf(f[i][2 * j], f[i][2 * j + 1]));
       }
@@ -138,9 +142,19 @@ dynamic_quant_ext_rows(const T* __restrict__ x, const ST* __restrict__ smooth, c
       // A row whose values sit far from zero compared with their spread has a huge offset; the sum with the
       // offset then rounds coarsely and can leave [-128, 127], which only the clamping path handles.
       const float inv = fabsf(offset) < 30000.0f ? quant_inverse(scale) : __int_as_float(0x7fc00000);
+      if (scale == 0.0f) {
 #pragma unroll
-      for (int i = 0; i < ITERS; ++i)
-        if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8_asym(f[i], scale, inv, offset));
+        for (int i = 0; i < ITERS; ++i)
+          if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8_asym<2>(f[i], scale, inv, offset));
+      } else if (inv == inv) {
+#pragma unroll
+        for (int i = 0; i < ITERS; ++i)
+          if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8_asym<0>(f[i], scale, inv, offset));
+      } else {
+#pragma unroll
+        for (int i = 0; i < ITERS; ++i)
+          if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8_asym<1>(f[i], scale, inv, offset));
+      }
     } else {
       const float amax = fmaxf(fabsf(mx), fabsf(mn));
       const float scale = __fdiv_rn(amax, 127.0f);

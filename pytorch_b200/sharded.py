@@ -158,10 +158,11 @@ class PeerColumnGather:
         from . import _cabi
         _cabi.scatter_columns(self.full, self.peer_ptrs, self.lo, self.hi)
 
-    def push_copy_engine(self) -> None:
-        """The same push as one copy-engine transfer per peer on the current stream (no SM involved)."""
+    def push_copy_engine(self, part: int = 0, parts: int = 1) -> None:
+        """The same push as one copy-engine transfer per peer on the current stream (no SM involved);
+        ``part`` of ``parts`` takes every ``parts``-th peer of the rank-staggered order."""
         from . import _cabi
-        _cabi.copy_columns(self.full, self.peer_ptrs, self.lo, self.hi)
+        _cabi.copy_columns(self.full, self.peer_ptrs[part::parts], self.lo, self.hi)
 
     def finish(self) -> torch.Tensor:
         self.peers.barrier()
@@ -188,14 +189,20 @@ class PipelinedExchange:
     queued on the side stream through :meth:`before_next_barrier`, before this rank joins the barrier of step
     i+1: peers write that matrix again in their step i+2, which they start once that barrier has passed."""
 
-    def __init__(self, peers: PeerGroup, gathers, device):
+    def __init__(self, peers: PeerGroup, gathers, device, copy_streams: int = 1):
         self.peers, self.gathers = peers, list(gathers)
-        self.side = torch.cuda.Stream(device=device)
+        # The copies to different peers can be spread over several streams (the barrier follows on the first).
+        # One stream is the default: with two, the ranks' rank-staggered transfers no longer stay in step, two
+        # senders meet at one receiver, and the four-GPU step measured 0.73 ms against 0.67 ms.
+        self.sides = [torch.cuda.Stream(device=device) for _ in range(max(1, min(copy_streams, peers.world - 1)))]
+        self.side = self.sides[0]
         nbuf = len(self.gathers[0].bufs)
         assert nbuf >= 2 and all(len(g.bufs) == nbuf for g in self.gathers)
         self._done = [torch.cuda.Event() for _ in range(nbuf)]
         self._produced = [[torch.cuda.Event() for _ in self.gathers] for _ in range(nbuf)]
+        self._copied = [[torch.cuda.Event() for _ in self.sides[1:]] for _ in range(nbuf)]
         self._steps = 0
+        self._prev_done = None
 
     def begin_step(self) -> None:
         """Before the first kernel that writes this step's result buffers."""
@@ -207,9 +214,12 @@ class PipelinedExchange:
         g = self.gathers[index]
         ev = self._produced[g.cur][index]
         ev.record(torch.cuda.current_stream())
-        with torch.cuda.stream(self.side):
-            self.side.wait_event(ev)
-            g.push_copy_engine()
+        for j, st in enumerate(self.sides):
+            with torch.cuda.stream(st):
+                st.wait_event(ev)
+                if j > 0 and self._prev_done is not None:
+                    st.wait_event(self._prev_done)        # like the first stream: not before the previous step's barrier
+                g.push_copy_engine(j, len(self.sides))
 
     def before_next_barrier(self, event: torch.cuda.Event) -> None:
         """A reader of an earlier step's gathered matrix has recorded ``event`` when it was done."""
@@ -217,16 +227,21 @@ class PipelinedExchange:
 
     def end_step(self) -> torch.cuda.Event:
         b = self.gathers[0].cur
+        for j, st in enumerate(self.sides[1:]):
+            self._copied[b][j].record(st)
+            self.side.wait_event(self._copied[b][j])
         with torch.cuda.stream(self.side):
             self.peers.barrier()
             self._done[b].record(self.side)
         for g in self.gathers:
             g.advance()
         self._steps += 1
+        self._prev_done = self._done[b]
         return self._done[b]
 
     def drain(self) -> None:
-        torch.cuda.current_stream().wait_stream(self.side)
+        for st in self.sides:
+            torch.cuda.current_stream().wait_stream(st)
 
 
 class LocalOutput:
