@@ -81,9 +81,12 @@ __device__ __forceinline__ float quant_inverse(float scale) {
 // so no clamp is needed.  No branch, no division; the four steps are packed two-wide fp32 instructions
 // (fma.rn.f32x2 and friends of sm_100), each lane rounded exactly like the scalar instruction, which halves
 // the issue slots of a kernel that is bound by instruction issue, not by arithmetic.
+// EXACT = false: the refinement above (inv is a finite reciprocal or 0); EXACT = true: true divisions (inv is
+// NaN).  The choice is the same for a whole row, so callers branch once per row, not once per vector.
+template <bool EXACT>
 __device__ __forceinline__ uint2 quantize8(const float2 (&f)[4], float scale, float inv) {
   uint32_t u[8];
-  if (inv == inv) {
+  if (!EXACT) {
     const float2 inv2 = make_float2(inv, inv), nscale2 = make_float2(-scale, -scale);
     const float2 magic2 = make_float2(12582912.0f, 12582912.0f);
 #pragma unroll
@@ -109,10 +112,22 @@ __device__ __forceinline__ uint2 quantize8(const float2 (&f)[4], float scale, fl
 }
 
 // The same for callers that hold eight separate floats.
+template <bool EXACT>
 __device__ __forceinline__ uint2 quantize8(const float (&f)[8], float scale, float inv) {
   const float2 g[4] = {{f[0], f[1]}, {f[2], f[3]}, {f[4], f[5]}, {f[6], f[7]}};
-  return quantize8(g, scale, inv);
+  return quantize8<EXACT>(g, scale, inv);
 }
+
+// RN(amax / 127), the row's scale, without the division routine: the same refinement with the constant
+// reciprocal.  Equal to the IEEE quotient for every float from 1e-30 up (checked exhaustively on the host);
+// smaller maxima take the division.
+__device__ __forceinline__ float scale_of_amax(float amax) {
+  if (amax < 1e-30f) return __fdiv_rn(amax, 127.0f);
+  const float r = __uint_as_float(0x3C010204u);          // RN(1/127)
+  const float q0 = __fmul_rn(amax, r);
+  return __fmaf_rn(__fmaf_rn(-q0, 127.0f, amax), r, q0);
+}
+
 template <typename ST>
 __device__ __forceinline__ void load_smooth8(const ST* p, float (&s)[8]) {
   float2 t[4];
@@ -150,19 +165,23 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // next row are issued before the arithmetic of the current one.  The fp32 products x*smooth are
 // formed once, in the max pass, and kept in registers for the quantisation pass.  FULL means that
 // every thread's every vector is inside the row (k == 8 * ITERS * blockDim): no bounds predicates.
-template <typename T, typename ST, int ITERS, bool SMOOTH, bool FULL>
-__global__ void __launch_bounds__(ITERS == 4 ? 1024 : 512) dynamic_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth,
-                                                         int8_t* __restrict__ y, float* __restrict__ scale_out,
-                                                         int64_t rows, int k) {
+// TH is the CTA size when it is one of the common ones (then every load, store and smooth-scale address is a
+// per-thread base plus a compile-time offset), else 0 (taken from blockDim).
+template <typename T, typename ST, int ITERS, bool SMOOTH, bool FULL, int TH = 0>
+__global__ void __launch_bounds__(TH ? TH : (ITERS == 4 ? 1024 : 512), TH == 256 ? 4 : 1)
+dynamic_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth, int8_t* __restrict__ y,
+                   float* __restrict__ scale_out, int64_t rows, int k) {
   __shared__ float red[2][32];
   const int nvec = k >> 3;
+  const int nth = TH ? TH : (int)blockDim.x;
   uint4 nxt[ITERS];
   float2 f[ITERS][4];
+  const ST* sm_base = smooth + (int64_t)threadIdx.x * 8;
   auto load_row = [&](int64_t row) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * k) + threadIdx.x;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i)
-      nxt[i] = (FULL || threadIdx.x + i * blockDim.x < nvec) ? ld_stream(xr + i * blockDim.x) : make_uint4(0, 0, 0, 0);
+      nxt[i] = (FULL || threadIdx.x + i * nth < nvec) ? ld_stream(xr + i * nth) : make_uint4(0, 0, 0, 0);
   };
   int64_t row = blockIdx.x;
   if (row < rows) load_row(row);
@@ -171,20 +190,26 @@ __global__ void __launch_bounds__(ITERS == 4 ? 1024 : 512) dynamic_quant_rows(co
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
-      const int v = threadIdx.x + i * blockDim.x;
+      const int v = threadIdx.x + i * nth;
       float2 sm[4] = {{1.0f, 1.0f}, {1.0f, 1.0f}, {1.0f, 1.0f}, {1.0f, 1.0f}};     // past the row: 0 * 1
-      if (SMOOTH && (FULL || v < nvec)) load_smooth8(smooth + v * 8, sm);
+      if (SMOOTH && (FULL || v < nvec)) load_smooth8(sm_base + i * nth * 8, sm);
       products8<T, SMOOTH>(nxt[i], sm, f[i], amax);
     }
     if (row + gridDim.x < rows) load_row(row + gridDim.x);   // in flight during the reduction and quantisation
     amax = block_max(amax, red[par]);
-    const float scale = __fdiv_rn(amax, 127.0f);
+    const float scale = scale_of_amax(amax);
     if (threadIdx.x == 0) scale_out[row] = scale;
     const float inv = quant_inverse(scale);
     uint2* yr = reinterpret_cast<uint2*>(y + row * k) + threadIdx.x;
+    if (inv == inv) {
 #pragma unroll
-    for (int i = 0; i < ITERS; ++i)
-      if (FULL || threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8(f[i], scale, inv));
+      for (int i = 0; i < ITERS; ++i)
+        if (FULL || threadIdx.x + i * nth < nvec) st_stream(yr + i * nth, quantize8<false>(f[i], scale, inv));
+    } else {
+#pragma unroll
+      for (int i = 0; i < ITERS; ++i)
+        if (FULL || threadIdx.x + i * nth < nvec) st_stream(yr + i * nth, quantize8<true>(f[i], scale, inv));
+    }
   }
 }
 
@@ -240,18 +265,23 @@ int launch_dq(const void* x, const void* smooth, int8_t* y, float* scale, int64_
   threads = (int)ceil_div(threads, 32) * 32;
   const bool full = (int64_t)threads * iters == nvec;
   int per_sm = 1;
-#define B200Q_DQ_LAUNCH(I, F)                                                                                 \
+#define B200Q_DQ_LAUNCH(I, F, TH)                                                                             \
   {                                                                                                            \
-    auto kern = dynamic_quant_rows<T, ST, I, SMOOTH, F>;                                                       \
+    auto kern = dynamic_quant_rows<T, ST, I, SMOOTH, F, TH>;                                                   \
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0);                                  \
     const int64_t cap = (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);                                       \
     kern<<<(unsigned)(rows < cap ? rows : cap), threads, 0, st>>>(xp, sp, y, scale, rows, (int)k);            \
   }
 #define B200Q_DQ_CASE(I)                                  \
   case I:                                                 \
-    if (full) B200Q_DQ_LAUNCH(I, true) else B200Q_DQ_LAUNCH(I, false) \
+    if (full) B200Q_DQ_LAUNCH(I, true, 0) else B200Q_DQ_LAUNCH(I, false, 0) \
     break;
-  switch (iters) {
+  // The common full-row shapes (k = 2048 * iters, 7168 * iters, 8192 * iters) with the CTA size compiled in.
+  if (full && iters == 4 && threads == 256) B200Q_DQ_LAUNCH(4, true, 256)
+  else if (full && iters == 4 && threads == 896) B200Q_DQ_LAUNCH(4, true, 896)
+  else if (full && iters == 4 && threads == 1024) B200Q_DQ_LAUNCH(4, true, 1024)
+  else if (full && iters == 2 && threads == 256) B200Q_DQ_LAUNCH(2, true, 256)
+  else switch (iters) {
     B200Q_DQ_CASE(1)
     B200Q_DQ_CASE(2)
     B200Q_DQ_CASE(4)

@@ -157,12 +157,18 @@ dynamic_quant_ext_rows(const T* __restrict__ x, const ST* __restrict__ smooth, c
       }
     } else {
       const float amax = fmaxf(fabsf(mx), fabsf(mn));
-      const float scale = __fdiv_rn(amax, 127.0f);
+      const float scale = scale_of_amax(amax);
       if (threadIdx.x == 0) scale_out[row] = scale;
       const float inv = quant_inverse(scale);
+      if (inv == inv) {
 #pragma unroll
-      for (int i = 0; i < ITERS; ++i)
-        if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8(f[i], scale, inv));
+        for (int i = 0; i < ITERS; ++i)
+          if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8<false>(f[i], scale, inv));
+      } else {
+#pragma unroll
+        for (int i = 0; i < ITERS; ++i)
+          if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8<true>(f[i], scale, inv));
+      }
     }
   }
 }

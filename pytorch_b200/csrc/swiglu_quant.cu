@@ -86,13 +86,19 @@ swiglu_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth, int8_t
     }
     if (row + gridDim.x < rows) load_row(row + gridDim.x);   // in flight during the reduction and quantisation
     amax = block_max(amax, red[par]);
-    const float scale = __fdiv_rn(amax, 127.0f);
+    const float scale = scale_of_amax(amax);
     if (threadIdx.x == 0) scale_out[row] = scale;
     const float inv = quant_inverse(scale);
     uint2* yr = reinterpret_cast<uint2*>(y + row * f) + threadIdx.x;
+    if (inv == inv) {
 #pragma unroll
-    for (int i = 0; i < ITERS; ++i)
-      if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8(act[i], scale, inv));
+      for (int i = 0; i < ITERS; ++i)
+        if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8<false>(act[i], scale, inv));
+    } else {
+#pragma unroll
+      for (int i = 0; i < ITERS; ++i)
+        if (threadIdx.x + i * blockDim.x < nvec) st_stream(yr + i * blockDim.x, quantize8<true>(act[i], scale, inv));
+    }
   }
 }
 
