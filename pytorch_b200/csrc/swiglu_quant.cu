@@ -9,24 +9,36 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace b200q {
 namespace {
 
+// Hardware reciprocal for operands in [1, 2^126]: the result is a normal number, so the flush-to-zero form
+// (which skips the rescaling of the full-range form) returns the same value.
 __device__ __forceinline__ float rcp_approx(float d) {
   float y;
-  asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(d));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(d));
   return y;
 }
 
-// (silu(a.x) * b.x, silu(a.y) * b.y) with silu(a) = a * (1 / (1 + exp(-a))).  The exponent is capped at 80, so
-// the sum stays a normal number (for a < -80 the result is below 2e-33 in magnitude either way).  The
-// reciprocal of a normal number: the hardware approximation (within one ulp) and one Newton step in two
-// fused multiply-adds, which rounds like an IEEE division of 1 by the sum without that routine's checks for
-// special operands.  Sums, products and the Newton step run as packed two-wide fp32 instructions.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// (silu(a.x) * b.x, silu(a.y) * b.y) with silu(a) = a * (1 / (1 + exp(-a))).  exp(-a) is the hardware
+// 2^x of -a * log2(e) (what __expf computes, without its rescaling for results below the normal range, which
+// vanish next to the 1 they are added to); the exponent is capped at 115 = 80 * log2(e), so the sum stays a
+// normal number (for a < -80 the result is below 2e-33 in magnitude either way).  The reciprocal of a normal
+// number: the hardware approximation (within one ulp) and one Newton step in two fused multiply-adds, which
+// rounds like an IEEE division of 1 by the sum without that routine's checks for special operands.  Sums,
+// products and the Newton step run as packed two-wide fp32 instructions.
 __device__ __forceinline__ float2 silu_mul2(float2 a, float2 b) {
   const float2 one = make_float2(1.0f, 1.0f);
-  const float2 d = __fadd2_rn(one, make_float2(__expf(fminf(-a.x, 80.0f)), __expf(fminf(-a.y, 80.0f))));
+  const float2 t = __fmul2_rn(a, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+  const float2 d = __fadd2_rn(one, make_float2(ex2_approx(fminf(t.x, 115.0f)), ex2_approx(fminf(t.y, 115.0f))));
   const float2 y0 = make_float2(rcp_approx(d.x), rcp_approx(d.y));
   const float2 err = __ffma2_rn(make_float2(-d.x, -d.y), y0, one);
   const float2 s = __ffma2_rn(y0, err, y0);
@@ -84,7 +96,23 @@ swiglu_quant_rows(const T* __restrict__ x, const ST* __restrict__ smooth, int8_t
         amax = fmaxf(amax, fmaxf(fabsf(r.x), fabsf(r.y)));
       }
     }
-    if (row + gridDim.x < rows) load_row(row + gridDim.x);   // in flight during the reduction and quantisation
+    if (row + gridDim.x < rows) {
+      load_row(row + gridDim.x);                             // in flight during the reduction and quantisation
+      if (!PREFETCH && (threadIdx.x & 7) == 0) {
+        // Wide rows: no registers to spare for the next row, so its lines are at least brought into L2 while this
+        // row is reduced and quantised (one prefetch per 128-byte line, by every eighth thread).
+        const char* na = reinterpret_cast<const char*>(x + (row + gridDim.x) * 2 * f + act_offset);
+        const char* nb = reinterpret_cast<const char*>(x + (row + gridDim.x) * 2 * f + gate_offset);
+#pragma unroll
+        for (int i = 0; i < ITERS; ++i) {
+          const int v = threadIdx.x + i * blockDim.x;
+          if (v < nvec) {
+            prefetch_l2(na + (int64_t)v * 16);
+            prefetch_l2(nb + (int64_t)v * 16);
+          }
+        }
+      }
+    }
     amax = block_max(amax, red[par]);
     const float scale = scale_of_amax(amax);
     if (threadIdx.x == 0) scale_out[row] = scale;

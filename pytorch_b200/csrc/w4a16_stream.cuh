@@ -69,9 +69,6 @@ __device__ __forceinline__ const uint32_t* add_u32(const char* p, uint32_t off) 
   asm("mad.wide.u32 %0, %1, 1, %2;" : "=l"(r) : "r"(off), "l"(reinterpret_cast<uint64_t>(p)));
   return reinterpret_cast<const uint32_t*>(r);
 }
-__device__ __forceinline__ void prefetch_l2(const void* p) {
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-}
 
 // Accumulator register of lane (gid, tig) that holds token tl of the CTA's token block and channel cl
 // of its column strip.  The inverse of the operand arrangement described above.
