@@ -116,15 +116,24 @@ __global__ void __launch_bounds__(256, 3) anti_quant_vec_kernel(const void* __re
       if (BITS == 8) {
         const uint32_t w[4] = {q[u].x ^ 0x80808080u, q[u].y ^ 0x80808080u, q[u].z ^ 0x80808080u, q[u].w ^ 0x80808080u};
 #pragma unroll
-        for (int j = 0; j < 16; j += 2)
-          o[j >> 1] = aq_pack<OT>(__fmul_rn(__fadd_rn(aq_byte_to_float(w[j >> 2], j & 3), of[j]), sc[j]),
-                                  __fmul_rn(__fadd_rn(aq_byte_to_float(w[j >> 2], (j & 3) + 1), of[j + 1]), sc[j + 1]));
+        for (int j = 0; j < 16; j += 2) {
+          // packed two-wide fp32: exact subtraction of the bias, rounded sum with the offset, rounded product
+          const float2 raw = make_float2(__uint_as_float(__byte_perm(w[j >> 2], 0x4B000000u, 0x7440 | (j & 3))),
+                                         __uint_as_float(__byte_perm(w[j >> 2], 0x4B000000u, 0x7440 | ((j & 3) + 1))));
+          const float2 v = __fadd2_rn(raw, make_float2(-8388736.0f, -8388736.0f));
+          const float2 r = __fmul2_rn(__fadd2_rn(v, make_float2(of[j], of[j + 1])), make_float2(sc[j], sc[j + 1]));
+          o[j >> 1] = aq_pack<OT>(r.x, r.y);
+        }
       } else {
         const uint32_t w[2] = {q[u].x ^ 0x88888888u, q[u].y ^ 0x88888888u};
 #pragma unroll
-        for (int j = 0; j < 16; j += 2)
-          o[j >> 1] = aq_pack<OT>(__fmul_rn(__fadd_rn(aq_nibble_to_float(w[j >> 3], j & 7), of[j]), sc[j]),
-                                  __fmul_rn(__fadd_rn(aq_nibble_to_float(w[j >> 3], (j & 7) + 1), of[j + 1]), sc[j + 1]));
+        for (int j = 0; j < 16; j += 2) {
+          const float2 raw = make_float2(__uint_as_float(((w[j >> 3] >> (4 * (j & 7))) & 0xFu) | 0x4B000000u),
+                                         __uint_as_float(((w[j >> 3] >> (4 * ((j & 7) + 1))) & 0xFu) | 0x4B000000u));
+          const float2 v = __fadd2_rn(raw, make_float2(-8388616.0f, -8388616.0f));
+          const float2 r = __fmul2_rn(__fadd2_rn(v, make_float2(of[j], of[j + 1])), make_float2(sc[j], sc[j + 1]));
+          o[j >> 1] = aq_pack<OT>(r.x, r.y);
+        }
       }
       uint4* dst = reinterpret_cast<uint4*>(out) + 2 * (r * vec_per_row + cv);
       __stcs(dst, make_uint4(o[0], o[1], o[2], o[3]));
