@@ -203,11 +203,19 @@ class PipelinedExchange:
         self._copied = [[torch.cuda.Event() for _ in self.sides[1:]] for _ in range(nbuf)]
         self._steps = 0
         self._prev_done = None
+        self._readers = [[] for _ in range(nbuf)]
+        self._last_b = 0
 
     def begin_step(self) -> None:
-        """Before the first kernel that writes this step's result buffers."""
+        """Before the first kernel that writes this step's result buffers: their last use (the copies out of
+        them two steps ago, and every registered reader of that step's gathered matrices) must be over."""
+        b = self.gathers[0].cur
+        cur = torch.cuda.current_stream()
         if self._steps >= len(self._done):
-            torch.cuda.current_stream().wait_event(self._done[self.gathers[0].cur])
+            cur.wait_event(self._done[b])
+        for ev in self._readers[b]:
+            cur.wait_event(ev)
+        self._readers[b] = []
 
     def produced(self, index: int) -> None:
         """The GEMM of gather ``index`` has been queued on the current stream."""
@@ -222,8 +230,11 @@ class PipelinedExchange:
                 g.push_copy_engine(j, len(self.sides))
 
     def before_next_barrier(self, event: torch.cuda.Event) -> None:
-        """A reader of an earlier step's gathered matrix has recorded ``event`` when it was done."""
+        """A reader of the gathered matrices of the step that ended last has recorded ``event`` when it was done:
+        this rank joins the next barrier only after it (peers write those matrices again once that barrier has
+        passed), and this rank's own kernels write them again only after it (see :meth:`begin_step`)."""
         self.side.wait_event(event)
+        self._readers[self._last_b].append(event)
 
     def end_step(self) -> torch.cuda.Event:
         b = self.gathers[0].cur
@@ -237,6 +248,7 @@ class PipelinedExchange:
             g.advance()
         self._steps += 1
         self._prev_done = self._done[b]
+        self._last_b = b
         return self._done[b]
 
     def drain(self) -> None:

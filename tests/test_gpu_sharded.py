@@ -113,6 +113,34 @@ def _rank_main(rank, world, port, results):
         dist.barrier()
         for full in fulls[-2:]:                           # the two result matrices hold the last two steps
             ok = ok and torch.equal(full.cpu().view(torch.int16), want.view(torch.int16))
+        # ... with a reader of every step's gathered matrix (a device-to-host copy on a third stream) and inputs that
+        # change from step to step: a matrix overwritten too early by a peer's later step would show up as a mismatch
+        xs = [workloads.w8a8_linear(m, k, n, 500 + i)["x"] for i in range(3)]
+        wants = []
+        for xi in xs:
+            qi, si = oracle.dynamic_quant(xi, d["smooth_scales"])
+            wants.append(oracle.quant_matmul(qi, d["x2"], d["scale"], pertoken_scale=si, output_dtype=torch.bfloat16))
+        xs_dev = [xi.to(dev) for xi in xs]
+        reader = torch.cuda.Stream(device=dev)
+        host = [torch.empty((m, n), dtype=torch.bfloat16).pin_memory() for _ in range(7)]
+        for step in range(7):
+            pipe.begin_step()
+            nop.quant(xs_dev[step % 3])
+            nop.matmul(push=False)
+            pipe.produced(0)
+            full = gat.full
+            done = pipe.end_step()
+            with torch.cuda.stream(reader):
+                reader.wait_event(done)
+                host[step].copy_(full, non_blocking=True)
+                read = torch.cuda.Event()
+                read.record(reader)
+            pipe.before_next_barrier(read)
+        pipe.drain()
+        torch.cuda.synchronize()
+        dist.barrier()
+        for step in range(7):
+            ok = ok and torch.equal(host[step].view(torch.int16), wants[step % 3].view(torch.int16))
         # collective-fused operators against the oracle of all ranks' inputs (same seed on every rank)
         g = torch.Generator().manual_seed(5)
         mm, kk, nn = 128, 256, 256
