@@ -156,6 +156,18 @@ __device__ __forceinline__ uint32_t nibbles_to_x2(uint32_t t) {
   return *reinterpret_cast<uint32_t*>(&w);
 }
 
+// Two int8 values, bytes ba and bb of a word whose bytes were biased by 128 (w ^ 0x80808080), as exact 16-bit
+// floats without the integer-to-float converter (a quarter-rate unit): each byte goes into the mantissa of
+// 2^23 by one byte-permute, one packed fp32 subtraction removes 2^23 + 128 exactly, one packed conversion
+// rounds to the 16-bit type (exact: |value| <= 128).
+template <typename XT>
+__device__ __forceinline__ uint32_t bytes_to_x2(uint32_t w_biased, int ba, int bb) {
+  const float2 raw = make_float2(__uint_as_float(__byte_perm(w_biased, 0x4B000000u, 0x7440 | ba)),
+                                 __uint_as_float(__byte_perm(w_biased, 0x4B000000u, 0x7440 | bb)));
+  const float2 v = __fadd2_rn(raw, make_float2(-8388736.0f, -8388736.0f));
+  return X2<XT>::pack(v.x, v.y);
+}
+
 // Fetches this thread's eight per-channel scale and offset values of group g (raw 16-bit values;
 // channels beyond n read as zero).  Kept separate from pair_params8 so that the loads for the next
 // K block can be in flight while the current one is dequantised.
@@ -274,13 +286,10 @@ __device__ __forceinline__ void dequant_tile(uint32_t raw, uint32_t b_tile, int 
             o[j] = add_mul2<XT, HAS_OFF>(nibbles_to_x2<XT>(v[i].x >> (4 * j)), of2[j], sc2[j]);
           }
         } else {
-          const uint32_t w2[2] = {v[i].x, v[i].y};
+          const uint32_t w2[2] = {v[i].x ^ 0x80808080u, v[i].y ^ 0x80808080u};
 #pragma unroll
-          for (int j = 0; j < 8; j += 2) {
-            const float a = (float)(int8_t)(w2[j >> 2] >> (8 * (j & 3)));
-            const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
-            o[j >> 1] = add_mul2<XT, HAS_OFF>(X2<XT>::pack(a, b), of2[j >> 1], sc2[j >> 1]);
-          }
+          for (int j = 0; j < 8; j += 2)
+            o[j >> 1] = add_mul2<XT, HAS_OFF>(bytes_to_x2<XT>(w2[j >> 2], j & 3, (j + 1) & 3), of2[j >> 1], sc2[j >> 1]);
         }
         sts_u128(dst + (b0 + i) * 1024, o[0], o[1], o[2], o[3]);
       }
@@ -311,14 +320,11 @@ __device__ __forceinline__ void dequant_tile(uint32_t raw, uint32_t b_tile, int 
       }
 #pragma unroll
       for (int i = 0; i < BATCH; ++i) {
-        const uint32_t w2[2] = {v[i].x, v[i].y};
+        const uint32_t w2[2] = {v[i].x ^ 0x80808080u, v[i].y ^ 0x80808080u};
         uint32_t o[4];
 #pragma unroll
-        for (int j = 0; j < 8; j += 2) {
-          const float a = (float)(int8_t)(w2[j >> 2] >> (8 * (j & 3)));
-          const float b = (float)(int8_t)(w2[j >> 2] >> (8 * ((j + 1) & 3)));
-          o[j >> 1] = add_mul2<XT, HAS_OFF>(X2<XT>::pack(a, b), o2[i], s2[i]);
-        }
+        for (int j = 0; j < 8; j += 2)
+          o[j >> 1] = add_mul2<XT, HAS_OFF>(bytes_to_x2<XT>(w2[j >> 2], j & 3, (j + 1) & 3), o2[i], s2[i]);
         sts_u128(dst + (b0 + i) * 4 * 1024, o[0], o[1], o[2], o[3]);
       }
     }
